@@ -38,12 +38,12 @@ def known_architectures() -> list[str]:
 
 
 def architecture_of(config: Mapping[str, Any]) -> Architecture:
-    names = config.get("architectures") or []
+    names = config.get("architectures") or config.get("architecture") or []   # a list, or one name
     if isinstance(names, str):
         names = [names]
     if not names:
         raise KeyError(
-            'config.json has no "architectures" entry; known architectures: '
+            'config.json has no "architectures" (or "architecture") entry; known architectures: '
             + ", ".join(known_architectures())
         )
     for n in names:

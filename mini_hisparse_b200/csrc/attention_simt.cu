@@ -13,6 +13,15 @@
 // [kv_begin, kv_end).  split < 0: the normalised output is written to `out`.  split >= 0:
 // the CTA writes an un-normalised partial (max, sum, accumulator) and combine merges the
 // splits with the rule of reference/attention.py:11-20.
+//
+// Options that other mixers bring, all off by default:
+//   dv != d    values of another width than keys; a page then holds [keys: nkv][P][d] followed by
+//              [values: nkv][P][dv] (for dv == d that IS the layout [2][nkv][P][d])
+//   sink       one learned number per query head that joins the softmax's denominator as exp(sink_h)
+//              with no key and no value: the running (max, sum) starts at (sink_h, 1) instead of
+//              (-inf, 0), in the unsplit item or in split 0 only, so it counts once
+//   gate       the output row is multiplied by sigmoid(gate[t][h * dv + e]); the gate comes as the
+//              columns of a float32 product (split-K parts summed in order)
 #include "common.cuh"
 
 using namespace mhb;
@@ -38,16 +47,29 @@ struct AttnArgs {
     const int* tok_part_row;   // [T] first partial row of a token
     int num_items, width, nq, nkv, d, P, num_pages, window;
     float scale;
+    int dv;                    // value width (== d unless the mixer says otherwise)
+    const float* sink;         // [nq] or null
+    const float* gate;         // [gate_nsplit][T][gate_ld] or null
+    int gate_nsplit, gate_ld;
+    size_t gate_split_stride;
 };
+
+__device__ __forceinline__ float gate_of(const AttnArgs& a, int t, int col) {
+    if (!a.gate) return 1.f;
+    const size_t idx = (size_t)t * a.gate_ld + col;
+    float g = a.gate[idx];
+    for (int s = 1; s < a.gate_nsplit; ++s) g += a.gate[idx + (size_t)s * a.gate_split_stride];
+    return 1.f / (1.f + expf(-g));
+}
 
 template <typename CT, int DPL>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_simt_kernel(const AttnArgs a) {
     extern __shared__ float smem[];
-    const int d = a.d;
+    const int d = a.d, dv = a.dv;
     float* q_s = smem;                       // [R_TILE][d]
     float* k_s = q_s + R_TILE * d;           // [KT][d + 1]
-    float* v_s = k_s + KT * (d + 1);         // [KT][d]
+    float* v_s = k_s + KT * (d + 1);         // [KT][dv]
     __shared__ int row_pos[R_TILE];
 
     pdl_launch_dependents();
@@ -86,6 +108,11 @@ attention_simt_kernel(const AttnArgs a) {
         l[rs] = 0.f;
 #pragma unroll
         for (int i = 0; i < DPL; ++i) acc[rs][i] = 0.f;
+        const int r = rs * WARPS + warp;
+        if (a.sink && split <= 0 && r < nrows) {      // the sink counts once: here or in split 0
+            m[rs] = a.sink[kvh * groups + head0 + r % nheads];
+            l[rs] = 1.f;
+        }
     }
 
     const int* table = a.block_table + (size_t)seg * a.width;
@@ -99,17 +126,14 @@ attention_simt_kernel(const AttnArgs a) {
                 if (page >= a.num_pages) page = -1;
             }
             if (page >= 0) {
-                const size_t off = ((((size_t)page * 2) * a.nkv + kvh) * a.P + kp % a.P) * (size_t)d;
-                const size_t voff = off + (size_t)a.nkv * a.P * d;
-                for (int e = lane; e < d; e += 32) {
-                    k_s[j * (d + 1) + e] = to_float(cache[off + e]);
-                    v_s[j * d + e] = to_float(cache[voff + e]);
-                }
+                const size_t pbase = (size_t)page * a.nkv * a.P * (d + dv);
+                const size_t off = pbase + ((size_t)kvh * a.P + kp % a.P) * d;
+                const size_t voff = pbase + (size_t)a.nkv * a.P * d + ((size_t)kvh * a.P + kp % a.P) * dv;
+                for (int e = lane; e < d; e += 32) k_s[j * (d + 1) + e] = to_float(cache[off + e]);
+                for (int e = lane; e < dv; e += 32) v_s[j * dv + e] = to_float(cache[voff + e]);
             } else {
-                for (int e = lane; e < d; e += 32) {
-                    k_s[j * (d + 1) + e] = 0.f;
-                    v_s[j * d + e] = 0.f;
-                }
+                for (int e = lane; e < d; e += 32) k_s[j * (d + 1) + e] = 0.f;
+                for (int e = lane; e < dv; e += 32) v_s[j * dv + e] = 0.f;
             }
         }
         __syncthreads();
@@ -141,7 +165,7 @@ attention_simt_kernel(const AttnArgs a) {
 #pragma unroll
                 for (int i = 0; i < DPL; ++i) {
                     const int e = lane + 32 * i;
-                    if (e < d) acc[rs][i] = fmaf(pj, v_s[j * d + e], acc[rs][i]);
+                    if (e < dv) acc[rs][i] = fmaf(pj, v_s[j * dv + e], acc[rs][i]);
                 }
             }
         }
@@ -155,19 +179,19 @@ attention_simt_kernel(const AttnArgs a) {
         const int t = tok0 + r / nheads, h = kvh * groups + head0 + r % nheads;
         if (split < 0) {
             const float inv = l[rs] > 0.f ? 1.f / l[rs] : 0.f;
-            CT* o = (CT*)a.out + ((size_t)t * a.nq + h) * d;
+            CT* o = (CT*)a.out + ((size_t)t * a.nq + h) * dv;
 #pragma unroll
             for (int i = 0; i < DPL; ++i) {
                 const int e = lane + 32 * i;
-                if (e < d) o[e] = from_float<CT>(acc[rs][i] * inv);
+                if (e < dv) o[e] = from_float<CT>(acc[rs][i] * inv * gate_of(a, t, h * dv + e));
             }
         } else {
             const size_t prow = (size_t)a.tok_part_row[t] + split;
-            float* pa = a.part_acc + (prow * a.nq + h) * d;
+            float* pa = a.part_acc + (prow * a.nq + h) * dv;
 #pragma unroll
             for (int i = 0; i < DPL; ++i) {
                 const int e = lane + 32 * i;
-                if (e < d) pa[e] = acc[rs][i];
+                if (e < dv) pa[e] = acc[rs][i];
             }
             if (lane == 0) {
                 a.part_ml[(prow * a.nq + h) * 2 + 0] = m[rs];
@@ -184,7 +208,8 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_acc,
                                          const float* __restrict__ part_ml,
                                          const int* __restrict__ tok_part_row,
                                          const int* __restrict__ tok_nsplit, OT* __restrict__ out,
-                                         int nq, int d, int every) {
+                                         int nq, int d, int every, const float* __restrict__ gate,
+                                         int gate_nsplit, size_t gate_split_stride, int gate_ld) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x, h = blockIdx.y;
@@ -208,14 +233,21 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_acc,
             const float w = ms > -INFINITY ? expf(ms - M) : 0.f;
             o += w * part_acc[((row0 + s) * nq + h) * d + e];
         }
-        out[((size_t)t * nq + h) * d + e] = from_float<OT>(o * inv);
+        float g = 1.f;
+        if (gate) {
+            const size_t idx = (size_t)t * gate_ld + h * d + e;
+            float z = gate[idx];
+            for (int s = 1; s < gate_nsplit; ++s) z += gate[idx + (size_t)s * gate_split_stride];
+            g = 1.f / (1.f + expf(-z));
+        }
+        out[((size_t)t * nq + h) * d + e] = from_float<OT>(o * inv * g);
     }
 }
 
 template <typename CT>
 int launch_attention(const AttnArgs& a, int max_items, cudaStream_t stream) {
-    const int dpl = (a.d + 31) / 32;
-    const size_t smem = sizeof(float) * ((size_t)R_TILE * a.d + (size_t)KT * (a.d + 1) + (size_t)KT * a.d);
+    const int dpl = (a.dv + 31) / 32;
+    const size_t smem = sizeof(float) * ((size_t)R_TILE * a.d + (size_t)KT * (a.d + 1) + (size_t)KT * a.dv);
     dim3 grid(max_items, a.nkv);
 #define MHB_ATTN_CASE(N)                                                                        \
     case N: {                                                                                   \
@@ -232,7 +264,7 @@ int launch_attention(const AttnArgs& a, int max_items, cudaStream_t stream) {
     switch (dpl) {
         MHB_ATTN_CASE(1) MHB_ATTN_CASE(2) MHB_ATTN_CASE(3) MHB_ATTN_CASE(4)
         MHB_ATTN_CASE(5) MHB_ATTN_CASE(6) MHB_ATTN_CASE(7) MHB_ATTN_CASE(8)
-        default: return fail("attention: head_dim %d is larger than 256", a.d);
+        default: return fail("attention: a value width of %d is larger than 256", a.dv);
     }
 #undef MHB_ATTN_CASE
     return check_launch("attention_simt");
@@ -252,6 +284,30 @@ MHB_EXPORT int mhb_attention_simt(const void* q, const void* cache, void* out, i
     a.items = items; a.positions = positions; a.block_table = block_table;
     a.tok_part_row = tok_part_row; a.num_items = num_items; a.width = width; a.nq = nq;
     a.nkv = nkv; a.d = d; a.P = P; a.num_pages = num_pages; a.window = window; a.scale = scale;
+    a.dv = d; a.sink = nullptr; a.gate = nullptr; a.gate_nsplit = 1; a.gate_ld = 0; a.gate_split_stride = 0;
+    MHB_DISPATCH_DTYPE(dtype, CT, return launch_attention<CT>(a, max_items, stream));
+    return 0;
+}
+
+// The same with the options: values dv wide, a sink per query head, a gate on the output.
+MHB_EXPORT int mhb_attention_simt_ext(const void* q, const void* cache, void* out, int dtype,
+                                      float* part_acc, float* part_ml, const int* items, int num_items,
+                                      int max_items, const int* positions, const int* block_table,
+                                      int width, const int* tok_part_row, int nq, int nkv, int d, int dv, int P,
+                                      int num_pages, int window, float scale, const float* sink,
+                                      const float* gate, int gate_nsplit, long long gate_split_stride, int gate_ld,
+                                      cudaStream_t stream) {
+    if (max_items <= 0) return 0;
+    if (nkv <= 0 || nq % nkv) return fail("attention: %d query heads over %d KV heads", nq, nkv);
+    if (nkv > 65535) return fail("attention: too many KV heads");
+    if (d > 1024) return fail("attention: a key width of %d is larger than 1024", d);
+    AttnArgs a;
+    a.q = q; a.cache = cache; a.out = out; a.part_acc = part_acc; a.part_ml = part_ml;
+    a.items = items; a.positions = positions; a.block_table = block_table;
+    a.tok_part_row = tok_part_row; a.num_items = num_items; a.width = width; a.nq = nq;
+    a.nkv = nkv; a.d = d; a.P = P; a.num_pages = num_pages; a.window = window; a.scale = scale;
+    a.dv = dv; a.sink = sink; a.gate = gate; a.gate_nsplit = gate_nsplit; a.gate_ld = gate_ld;
+    a.gate_split_stride = (size_t)gate_split_stride;
     MHB_DISPATCH_DTYPE(dtype, CT, return launch_attention<CT>(a, max_items, stream));
     return 0;
 }
@@ -267,6 +323,22 @@ MHB_EXPORT int mhb_attention_combine(const float* part_acc, const float* part_ml
     const int threads = d >= 128 ? 128 : 32 * ((d + 31) / 32);
     MHB_DISPATCH_DTYPE(dtype, OT,
         launch_kernel(attention_combine_kernel<OT>, grid, dim3(threads), 0, stream, part_acc, part_ml,
-                      tok_part_row, tok_nsplit, (OT*)out, nq, d, every));
+                      tok_part_row, tok_nsplit, (OT*)out, nq, d, every, (const float*)nullptr, 1, (size_t)0, 0));
+    return check_launch("attention_combine");
+}
+
+// The merge with a gate on the output (see the options at the top); d is the VALUE width here.
+MHB_EXPORT int mhb_attention_combine_gated(const float* part_acc, const float* part_ml, const int* tok_part_row,
+                                           const int* tok_nsplit, void* out, int dtype, int T, int nq, int d,
+                                           int every, const float* gate, int gate_nsplit,
+                                           long long gate_split_stride, int gate_ld, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (every <= 0 && (!tok_part_row || !tok_nsplit)) return fail("attention_combine: no list of parts");
+    dim3 grid(T, nq);
+    const int threads = d >= 128 ? 128 : 32 * ((d + 31) / 32);
+    MHB_DISPATCH_DTYPE(dtype, OT,
+        launch_kernel(attention_combine_kernel<OT>, grid, dim3(threads), 0, stream, part_acc, part_ml,
+                      tok_part_row, tok_nsplit, (OT*)out, nq, d, every, gate, gate_nsplit,
+                      (size_t)gate_split_stride, gate_ld));
     return check_launch("attention_combine");
 }

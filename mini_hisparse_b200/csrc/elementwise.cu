@@ -23,31 +23,53 @@ __device__ __forceinline__ float load_split(const T* p, size_t idx, int nsplit, 
 }
 
 // ---- embedding ---------------------------------------------------------------------------
-// out[t, :] = table[tokens[t], :]   (mini_hisparse/model.py:166: plain lookup, no scaling)
+// out[t, :] = table[tokens[t], :] * scale   (mini_hisparse/model.py:166: plain lookup, scale 1; an
+// embedding with a scale multiplies in float32), and optionally a copy of the row in the compute dtype
 template <typename WT>
 __global__ void embed_kernel(const WT* __restrict__ table, const int* __restrict__ tokens,
-                             float* __restrict__ out, int H, int V, int* __restrict__ status) {
+                             float* __restrict__ out, int H, int V, int* __restrict__ status, float scale,
+                             __nv_bfloat16* __restrict__ copy) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
     const int tok = tokens[t];
     float* o = out + (size_t)t * H;
     if (tok < 0 || tok >= V) {  // the host validates ids; never read outside the table
-        for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = 0.f;
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            o[i] = 0.f;
+            if (copy) copy[(size_t)t * H + i] = __float2bfloat16_rn(0.f);
+        }
         if (threadIdx.x == 0 && status) atomicOr(status, 1);
         return;
     }
     const WT* row = table + (size_t)tok * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_float(row[i]);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = to_float(row[i]) * scale;
+        o[i] = v;
+        if (copy) copy[(size_t)t * H + i] = __float2bfloat16_rn(v);
+    }
+}
+
+static int launch_embed(const void* table, int table_dtype, const int* tokens, float* out, int T, int H, int V,
+                        int* status, float scale, void* copy, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    const int threads = H >= 1024 ? 256 : 128;
+    MHB_DISPATCH_DTYPE(table_dtype, WT,
+        launch_kernel(embed_kernel<WT>, dim3(T), dim3(threads), 0, stream, (const WT*)table, tokens, out, H, V, status,
+                      scale, (__nv_bfloat16*)copy));
+    return check_launch("embed");
 }
 
 MHB_EXPORT int mhb_embed(const void* table, int table_dtype, const int* tokens, float* out, int T,
                          int H, int V, int* status, cudaStream_t stream) {
-    if (T <= 0) return 0;
-    const int threads = H >= 1024 ? 256 : 128;
-    MHB_DISPATCH_DTYPE(table_dtype, WT,
-        launch_kernel(embed_kernel<WT>, dim3(T), dim3(threads), 0, stream, (const WT*)table, tokens, out, H, V, status));
-    return check_launch("embed");
+    return launch_embed(table, table_dtype, tokens, out, T, H, V, status, 1.f, nullptr, stream);
+}
+
+// The lookup times `scale`, and, if `copy` is given, the same rows once more in bfloat16 (what the
+// first block's products read when the block does not normalise its input).
+MHB_EXPORT int mhb_embed_scaled(const void* table, int table_dtype, const int* tokens, float* out, int T,
+                                int H, int V, int* status, float scale, void* copy, cudaStream_t stream) {
+    return launch_embed(table, table_dtype, tokens, out, T, H, V, status, scale, copy, stream);
 }
 
 // ---- (add +) RMSNorm -----------------------------------------------------------------------

@@ -100,7 +100,7 @@ class _Staging:
 class _PlanSlot:
     """One plan per step: the planner of the mixers of one page group whose plan keys are equal."""
 
-    gid: int
+    gid: object          # (kind of group, its index)
     key: object
     planner: StepPlanner
 
@@ -145,8 +145,9 @@ class BatchBuilder:
         with plan_key() and planner()); returns the index that cache_view() takes."""
         slot = None
         where = self.cache.entry_group[cache_entry] if cache_entry is not None else None
-        if where is not None and where[0] == "pages" and part is not None and part.plan_key() is not None:
-            gid, key = where[1], part.plan_key()
+        if where is not None and part is not None and part.plan_key() is not None:
+            # plans are shared inside one group of one kind (a page group or a state group)
+            gid, key = (where[0], where[1]), part.plan_key()
             for i, sl in enumerate(self.slots):
                 if sl.gid == gid and sl.key == key:
                     slot = i
@@ -297,7 +298,8 @@ class BatchBuilder:
                 meta.update(views["plans"][slot])
             return CacheView(g.need, g.gid, where[2], writable, storage,
                              page_size=self.cache.cfg.page_size, meta=meta)
-        return CacheView(g.need, g.gid, where[2], writable, storage)
+        meta = dict(views["plans"][slot]) if slot is not None else {}
+        return CacheView(g.need, g.gid, where[2], writable, storage, meta=meta)
 
 
 class ModelRunner:

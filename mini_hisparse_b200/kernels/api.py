@@ -79,13 +79,158 @@ def _contig(t: torch.Tensor, name: str):
 
 
 # ---------------------------------------------------------------------------------------
-def embed(table, tokens, out, status=None):
-    """out[t] = table[tokens[t]] as float32; ids outside the table give zeros and set status bit 0."""
+def embed(table, tokens, out, status=None, scale: float = 1.0, copy=None):
+    """out[t] = table[tokens[t]] * scale as float32; ids outside the table give zeros and set status
+    bit 0.  ``copy`` (bfloat16 [T, H]): the same rows once more, rounded, for a block whose products
+    read the stream itself."""
     lib = build.load("elementwise")
     T, H = out.shape
-    _check(lib, lib.mhb_embed(_ptr(table), c_int(dtype_code(table.dtype)), _ptr(tokens), _ptr(out),
-                              c_int(T), c_int(H), c_int(table.shape[0]), _ptr(status), _stream()),
-           "embed")
+    if scale == 1.0 and copy is None:
+        _check(lib, lib.mhb_embed(_ptr(table), c_int(dtype_code(table.dtype)), _ptr(tokens), _ptr(out),
+                                  c_int(T), c_int(H), c_int(table.shape[0]), _ptr(status), _stream()),
+               "embed")
+        return
+    if copy is not None and (copy.dtype != torch.bfloat16 or tuple(copy.shape) != (T, H) or not copy.is_contiguous()):
+        raise KernelError("embed: the copy must be a contiguous bfloat16 matrix of the output's shape")
+    _check(lib, lib.mhb_embed_scaled(_ptr(table), c_int(dtype_code(table.dtype)), _ptr(tokens), _ptr(out),
+                                     c_int(T), c_int(H), c_int(table.shape[0]), _ptr(status), c_float(scale),
+                                     _ptr(copy), _stream()), "embed")
+
+
+def norm_mix(x, weight, eps, *, delta=None, nsplit=1, split_stride=0, alpha=1.0, keep=0.0, copy=None):
+    """x <- keep * x + rms(alpha * x + delta) * weight, row by row in float32, in place; ``copy`` (compute
+    dtype, same shape) receives the new rows too.  alpha = 0 leaves x out of the norm (a normalised branch
+    that is ADDED to the stream: keep = 1); keep = 0 replaces the stream by the norm (norm after the sum).
+    ``delta`` may be ``nsplit`` float32 partial matrices ``split_stride`` elements apart."""
+    lib = build.load("postnorm")
+    R, H = x.shape
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("norm_mix: the stream must be a contiguous float32 matrix")
+    if delta is None and alpha == 0.0:
+        raise KernelError("norm_mix: nothing to normalise")
+    ddt = dtype_code(delta.dtype) if delta is not None else F32
+    cdt = dtype_code(copy.dtype) if copy is not None else F32
+    _check(lib, lib.mhb_norm_mix(_ptr(x), _ptr(delta), c_int(ddt), c_int(nsplit), c_longlong(split_stride),
+                                 _ptr(weight), c_float(eps), c_float(alpha), c_float(keep), _ptr(copy), c_int(cdt),
+                                 c_int(R), c_int(H), _stream()), "norm_mix")
+
+
+ACTIVATIONS = {"relu2": 0, "silu": 1, "gelu_tanh": 2, "copy": 3}
+
+
+def act_rows(z, out, act: str, nsplit=1, split_stride=0):
+    """out = act(z) element by element in float32; z may be split-K parts.  act: relu2 (the square of
+    relu), silu, gelu_tanh, copy (a conversion only)."""
+    lib = build.load("postnorm")
+    if act not in ACTIVATIONS:
+        raise KernelError(f"act_rows: unknown activation {act!r}; known: {sorted(ACTIVATIONS)}")
+    _check(lib, lib.mhb_act_rows(_ptr(z), c_int(dtype_code(z.dtype)), c_int(nsplit), c_longlong(split_stride),
+                                 _ptr(out), c_int(dtype_code(out.dtype)), c_longlong(out.numel()),
+                                 c_int(ACTIVATIONS[act]), _stream()), "act_rows")
+
+
+def table_gate(z, table, column0, tokens, out, nsplit=1, split_stride=0, status=None):
+    """out[t, j] = gelu_tanh(z[t, j]) * table[tokens[t], column0 + j]."""
+    lib = build.load("postnorm")
+    T, D = out.shape
+    if not table.is_contiguous() or not out.is_contiguous():
+        raise KernelError("table_gate: table and output must be contiguous")
+    _check(lib, lib.mhb_table_gate(_ptr(z), c_int(dtype_code(z.dtype)), c_int(nsplit), c_longlong(split_stride),
+                                   _ptr(table), c_int(dtype_code(table.dtype)), c_int(table.shape[1]),
+                                   c_int(column0), c_int(table.shape[0]), _ptr(tokens), _ptr(out),
+                                   c_int(dtype_code(out.dtype)), c_int(T), c_int(D), _ptr(status), _stream()),
+           "table_gate")
+
+
+def _gate_args(gate, gate_nsplit, gate_split_stride):
+    """(pointer, parts, stride between parts, row stride) of a gate that is a run of columns of a float32 product."""
+    if gate is None:
+        return c_void_p(0), c_int(1), c_longlong(0), c_int(0)
+    if gate.dtype != torch.float32 or gate.stride(-1) != 1:
+        raise KernelError("a gate must be float32 columns of a product")
+    return _ptr(gate), c_int(gate_nsplit), c_longlong(gate_split_stride), c_int(gate.stride(-2))
+
+
+def gated_rmsnorm(o, weight, eps, out, gate=None, gate_nsplit=1, gate_split_stride=0):
+    """out = rms(o) * weight * sigmoid(gate): o float32 [R, N]; ``gate`` [R, N] is a view of columns of
+    a float32 product (its parts ``gate_split_stride`` elements apart)."""
+    lib = build.load("postnorm")
+    R, N = o.shape
+    if o.dtype != torch.float32 or not o.is_contiguous() or not out.is_contiguous():
+        raise KernelError("gated_rmsnorm: o must be contiguous float32, out contiguous")
+    g = _gate_args(gate, gate_nsplit, gate_split_stride)
+    _check(lib, lib.mhb_gated_rmsnorm(_ptr(o), g[0], g[1], g[2], g[3], _ptr(weight), c_float(eps), _ptr(out),
+                                      c_int(dtype_code(out.dtype)), c_int(R), c_int(N), _stream()), "gated_rmsnorm")
+
+
+def qknorm_rope_append(qkv, q_weight, k_weight, eps, positions, tok_seg, block_table, inv_freq, rotary_dim, q_out,
+                       cache, *, nq, nkv, dk, dv, page_size, has_kv=True, nsplit=1, split_stride=0, status=None):
+    """RMS norm over the whole q projection and over the whole k projection, rotation of the first
+    ``rotary_dim`` elements of every head (pairs (i, i + rotary_dim/2)), q to ``q_out`` [T, nq dk], k and v
+    into the pages of ``cache`` (one layer's pool; a page holds [nkv][P][dk] keys then [nkv][P][dv] values).
+    ``qkv`` float32 [.., T, ld] holds [q | k | v | ...] per row; with ``has_kv`` False it holds [q | ...]
+    and nothing is appended."""
+    lib = build.load("postnorm")
+    T = q_out.shape[0]
+    if qkv.dtype != torch.float32 or qkv.stride(-1) != 1:
+        raise KernelError("qknorm_rope_append: the product must be float32 with contiguous rows")
+    if has_kv and (cache is None or cache.dtype != q_out.dtype or not cache.is_contiguous()):
+        raise KernelError("qknorm_rope_append: the pool must be contiguous and of the activations' dtype")
+    if rotary_dim and (inv_freq is None or inv_freq.numel() != rotary_dim // 2):
+        raise KernelError(f"qknorm_rope_append: {rotary_dim} rotated elements need {rotary_dim // 2} frequencies")
+    _check(lib, lib.mhb_qknorm_rope_append(
+        _ptr(qkv), c_int(nsplit), c_longlong(split_stride), c_int(qkv.stride(-2)), _ptr(q_weight), _ptr(k_weight),
+        c_float(eps), _ptr(positions), _ptr(tok_seg), _ptr(block_table), c_int(block_table.shape[-1]),
+        _ptr(inv_freq), c_int(rotary_dim), _ptr(q_out), _ptr(cache if has_kv else None), c_int(dtype_code(q_out.dtype)),
+        c_int(T), c_int(nq), c_int(nkv), c_int(dk), c_int(dv), c_int(page_size),
+        c_int(cache.shape[0] if has_kv else 0), c_int(1 if has_kv else 0), _ptr(status), _stream()),
+        "qknorm_rope_append")
+
+
+def _lightning_head(proj, q0, k0, v0, decay, state, out, ctx_arrays, H, dk, dv, nsplit, split_stride, writable):
+    tok_seg, seg_slot, positions = ctx_arrays
+    if proj.dtype != torch.float32 or proj.stride(-1) != 1 or state.dtype != torch.float32 or out.dtype != torch.float32:
+        raise KernelError("lightning: the product, the state and the output are float32")
+    if not state.is_contiguous() or not out.is_contiguous() or tuple(state.shape[1:]) != (H, dk, dv):
+        raise KernelError(f"lightning: the state must be contiguous [slots, {H}, {dk}, {dv}]")
+    return (_ptr(proj), c_int(nsplit), c_longlong(split_stride), c_int(proj.stride(-2)), c_int(q0), c_int(k0),
+            c_int(v0), _ptr(decay), _ptr(state), _ptr(out), _ptr(tok_seg), _ptr(seg_slot), _ptr(positions))
+
+
+def lightning_scan(proj, q0, k0, v0, decay, state, out, tok_seg, seg_slot, positions, *, heads, dk, dv, nsplit=1,
+                   split_stride=0, writable=True, max_tokens=0):
+    """Linear attention with decay, token by token, for every segment of at most ``max_tokens`` tokens
+    (0: all).  ``proj`` float32 [.., T, ld] holds silu's inputs: q at column q0, k at k0, v at v0, heads
+    side by side; ``state`` [slots, heads, dk, dv]; ``out`` float32 [T, heads * dv]."""
+    lib = build.load("lightning")
+    T, S = out.shape[0], seg_slot.shape[0]
+    head = _lightning_head(proj, q0, k0, v0, decay, state, out, (tok_seg, seg_slot, positions), heads, dk, dv,
+                           nsplit, split_stride, writable)
+    _check(lib, lib.mhb_lightning_scan(*head, c_int(T), c_int(S), c_int(heads), c_int(dk), c_int(dv),
+                                       c_int(1 if writable else 0), c_int(max_tokens), _stream()), "lightning_scan")
+
+
+def lightning_chunk_smem(dk: int, dv: int, chunk: int) -> int:
+    """Shared memory the chunked route needs for chunks of ``chunk`` tokens."""
+    lib = build.load("lightning")
+    lib.mhb_lightning_chunk_smem.restype = c_longlong
+    return int(lib.mhb_lightning_chunk_smem(c_int(dk), c_int(dv), c_int(chunk)))
+
+
+def lightning_chunked(proj, q0, k0, v0, decay, state, out, tok_seg, seg_slot, positions, chunks, num_chunks,
+                      seg_chunks, num_segs, scratch, chunk, *, heads, dk, dv, nsplit=1, split_stride=0, writable=True):
+    """The same for the listed segments, cut into the listed chunks of at most ``chunk`` tokens (4 ints
+    each: see csrc/lightning.cu); ``scratch`` float32 holds num_chunks * heads * dk * dv."""
+    lib = build.load("lightning")
+    T = out.shape[0]
+    if scratch.dtype != torch.float32 or scratch.numel() < num_chunks * heads * dk * dv:
+        raise KernelError("lightning_chunked: the scratch is too small")
+    head = _lightning_head(proj, q0, k0, v0, decay, state, out, (tok_seg, seg_slot, positions), heads, dk, dv,
+                           nsplit, split_stride, writable)
+    _check(lib, lib.mhb_lightning_chunked(*head, c_int(T), c_int(heads), c_int(dk), c_int(dv),
+                                          c_int(1 if writable else 0), _ptr(chunks), c_int(num_chunks),
+                                          _ptr(seg_chunks), c_int(num_segs), _ptr(scratch), c_int(chunk), _stream()),
+           "lightning_chunked")
 
 
 def add_rmsnorm(x, weight, eps, out, delta=None, nsplit=1, split_stride=0, rows=None):
@@ -283,10 +428,24 @@ def gemm_tc_qkv_rope(x, w, bias, cos_sin, positions, tok_seg, block_table, q_out
 
 
 def attention_simt(q, cache, out, part_acc, part_ml, items, num_items, max_items, positions,
-                   block_table, tok_part_row, *, nq, nkv, d, page_size, window=0, scale=None):
+                   block_table, tok_part_row, *, nq, nkv, d, page_size, window=0, scale=None, dv=None,
+                   sink=None, gate=None, gate_nsplit=1, gate_split_stride=0):
+    """CUDA-core attention over the items of a plan.  Options: ``dv`` values of another width than the
+    keys (a page then holds the keys of all KV heads followed by their values), ``sink`` float32 [nq]
+    (one extra term exp(sink_h) in the softmax's denominator), ``gate`` (the output is multiplied by its
+    sigmoid; columns of a float32 product)."""
     lib = build.load("attention_simt")
     if scale is None:
         scale = float(d) ** -0.5
+    if dv is not None or sink is not None or gate is not None:
+        g = _gate_args(gate, gate_nsplit, gate_split_stride)
+        _check(lib, lib.mhb_attention_simt_ext(
+            _ptr(q), _ptr(cache), _ptr(out), c_int(dtype_code(q.dtype)), _ptr(part_acc), _ptr(part_ml),
+            _ptr(items), c_int(num_items), c_int(max_items), _ptr(positions), _ptr(block_table),
+            c_int(block_table.shape[-1]), _ptr(tok_part_row), c_int(nq), c_int(nkv), c_int(d), c_int(dv or d),
+            c_int(page_size), c_int(cache.shape[0]), c_int(window or 0), c_float(scale), _ptr(sink),
+            g[0], g[1], g[2], g[3], _stream()), "attention")
+        return
     _check(lib, lib.mhb_attention_simt(
         _ptr(q), _ptr(cache), _ptr(out), c_int(dtype_code(q.dtype)), _ptr(part_acc), _ptr(part_ml),
         _ptr(items), c_int(num_items), c_int(max_items), _ptr(positions), _ptr(block_table),
@@ -424,11 +583,20 @@ def attention_tc(q, cache, out, items, num_items, positions, block_table, *, nq,
         c_int(cache.shape[0]), c_int(window or 0), c_float(scale), _ptr(status), _stream()), "attention_tc")
 
 
-def attention_combine(part_acc, part_ml, tok_part_row, tok_nsplit, out, *, nq, d, every=0):
+def attention_combine(part_acc, part_ml, tok_part_row, tok_nsplit, out, *, nq, d, every=0, gate=None,
+                      gate_nsplit=1, gate_split_stride=0):
     """Merge the parts of every token's attention.  ``every`` > 0: each token has exactly that many parts,
-    in the rows t * every ... of the partial buffers (the two index arrays may be None)."""
+    in the rows t * every ... of the partial buffers (the two index arrays may be None).  ``d`` is the
+    width of a head's output; ``gate``: see attention_simt."""
     lib = build.load("attention_simt")
     T = out.shape[0]
+    if gate is not None:
+        g = _gate_args(gate, gate_nsplit, gate_split_stride)
+        _check(lib, lib.mhb_attention_combine_gated(_ptr(part_acc), _ptr(part_ml), _ptr(tok_part_row),
+                                                    _ptr(tok_nsplit), _ptr(out), c_int(dtype_code(out.dtype)),
+                                                    c_int(T), c_int(nq), c_int(d), c_int(every), g[0], g[1], g[2],
+                                                    g[3], _stream()), "attention_combine")
+        return
     _check(lib, lib.mhb_attention_combine(_ptr(part_acc), _ptr(part_ml), _ptr(tok_part_row),
                                           _ptr(tok_nsplit), _ptr(out), c_int(dtype_code(out.dtype)),
                                           c_int(T), c_int(nq), c_int(d), c_int(every), _stream()),

@@ -1,2 +1,2 @@
-from . import qwen2  # noqa: F401  (registers Qwen2ForCausalLM)
+from . import koronex, qwen2  # noqa: F401  (register Koronex and Qwen2ForCausalLM)
 from .decoder import DecoderModel

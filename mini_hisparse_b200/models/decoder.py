@@ -13,7 +13,7 @@ import torch
 from ..kernels import api as K
 from ..parts.base import CacheView, Product, Runtime, StepContext
 from ..parts.registry import BLOCKS, EMBEDDINGS, HEADS, NORMS
-from ..parts.spec import ModelSpec, ParamSpec
+from ..parts.spec import ModelSpec, ParamSpec, join_name
 
 
 class DecoderModel:
@@ -21,6 +21,10 @@ class DecoderModel:
         self.spec, self.rt, self.config = spec, rt, config
         self.embedding = EMBEDDINGS.build(spec.embedding, rt=rt)
         self.blocks = [BLOCKS.get(layer.block)(layer, rt) for layer in spec.layers]
+        # parts of the model as a whole (a table every layer reads a slice of), handed to the blocks by key
+        self.shared = {key: EMBEDDINGS.build(part, rt=rt) for key, part, _ in spec.shared}
+        for block in self.blocks:
+            block.bind(self.shared)
         self.final_norm = NORMS.build(spec.final_norm, rt=rt)
         self.head = HEADS.build(spec.head, rt=rt)
         # cache entries: one per run entry that owns a cache
@@ -45,9 +49,11 @@ class DecoderModel:
     def named_parts(self):
         """(checkpoint prefix, part) for every part that stores tensors."""
         yield self.spec.embedding_name, self.embedding
+        for key, _, prefix in self.spec.shared:
+            yield prefix, self.shared[key]
         for layer, block in zip(self.spec.layers, self.blocks):
             for role, part in block.parts().items():
-                yield f"{layer.prefix}.{layer.name_of(role)}", part
+                yield join_name(layer.prefix, layer.name_of(role)), part
         yield self.spec.final_norm_name, self.final_norm
         yield self.spec.head_name, self.head
 
@@ -64,7 +70,7 @@ class DecoderModel:
         out = {}
         for prefix, part in self.named_parts():
             for local, ps in part.parameters().items():
-                out[f"{prefix}.{local}"] = ps
+                out[join_name(prefix, local)] = ps
         return out
 
     def finish_loading(self):
@@ -102,7 +108,10 @@ class DecoderModel:
         pending: Product | None = None
         for i, entry in enumerate(self.spec.order):
             view = caches[i]
-            pending = self.blocks[entry.layer].forward(x, pending, ctx, view)
+            block = self.blocks[entry.layer]
+            pending = block.forward(x, pending, ctx, view)
+            if not block.keeps_copy:
+                ctx.extras.pop("x_copy", None)     # whoever changed the stream did not keep its copy in step
             if observer is not None:
                 observer(i, x, pending)
         if observer is not None and pending is not None:

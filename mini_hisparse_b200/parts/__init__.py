@@ -1,5 +1,5 @@
 """Parts that layers are put together from.  Importing the package registers the built-in kinds."""
-from . import attention, block, embedding, feed_forward, norm, position  # noqa: F401
+from . import attention, block, embedding, feed_forward, lightning, norm, position, sink_attention  # noqa: F401
 from .base import (Block, CacheView, FeedForward, Mixer, Norm, Part, Product, Runtime, Segment, StepContext,
                    StepPlanner, Workspace)
 from .registry import (

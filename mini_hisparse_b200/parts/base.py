@@ -298,9 +298,14 @@ class Block:
     """
 
     mixer: "Mixer | None" = None
+    #: True if forward() leaves ctx.extras["x_copy"] (the stream's rows in the compute dtype) valid
+    keeps_copy = False
 
     def parts(self) -> dict[str, Part]:
         raise NotImplementedError
+
+    def bind(self, shared: dict[str, Part]) -> None:
+        """Receive the model's shared parts (ModelSpec.shared) by key; most arrangements need none."""
 
     def cache_need(self) -> CacheNeed | None:
         return self.mixer.cache_need() if self.mixer is not None else None

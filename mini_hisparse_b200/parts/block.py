@@ -1,6 +1,7 @@
 """Block arrangements: how a layer's norms, mixer and feed-forward are wired to the residual."""
 from __future__ import annotations
 
+from ..kernels import api as K
 from .base import Block, CacheView, Product, StepContext
 from .registry import FEED_FORWARDS, MIXERS, NORMS, register_block
 from .spec import LayerSpec
@@ -34,3 +35,64 @@ class PreNormBlock(Block):
         a = self.mixer.forward(h, ctx, cache)
         h = self.ff_norm.forward(x, ctx, delta=a)
         return self.feed_forward.forward(h, ctx)
+
+
+@register_block("post_norm")
+class PostNormBlock(Block):
+    """Norm AFTER the sum, with a scale on the stream:
+
+        x <- norm1(alpha x + mixer(x));   x <- norm2(alpha x + ff(x))  (if the layer has a feed-forward);
+        x <- x + side(x)                  (if the layer has a "side" part: a normalised branch of its own)
+
+    The sublayers read the stream itself, so every kernel that writes the stream also leaves its rows
+    in the compute dtype (ctx.extras["x_copy"]; the float32 path reads the stream directly).  Roles:
+    "mixer", "mixer_norm", and optionally "feed_forward" with "ff_norm", and "side".  Option: alpha.
+    Nothing is left pending: the block returns None.
+    """
+
+    keeps_copy = True
+
+    def __init__(self, spec: LayerSpec, rt):
+        self.spec = spec
+        self.alpha = float(spec.option("alpha", 1.0))
+        self.mixer = MIXERS.build(spec.part("mixer"), rt=rt)
+        self.mixer_norm = NORMS.build(spec.part("mixer_norm"), rt=rt)
+        self.feed_forward = self.ff_norm = self.side = None
+        if spec.has("feed_forward"):
+            self.feed_forward = FEED_FORWARDS.build(spec.part("feed_forward"), rt=rt)
+            self.ff_norm = NORMS.build(spec.part("ff_norm"), rt=rt)
+        if spec.has("side"):
+            self.side = FEED_FORWARDS.build(spec.part("side"), rt=rt)
+
+    def parts(self):
+        out = {"mixer_norm": self.mixer_norm, "mixer": self.mixer}
+        if self.feed_forward is not None:
+            out.update(ff_norm=self.ff_norm, feed_forward=self.feed_forward)
+        if self.side is not None:
+            out["side"] = self.side
+        return out
+
+    def bind(self, shared):
+        for part in self.parts().values():
+            if hasattr(part, "bind"):
+                part.bind(shared)
+
+    def forward(self, x, pending: Product | None, ctx: StepContext, cache: CacheView | None):
+        if pending is not None:          # the block before this one was of another arrangement
+            K.residual_add(x, pending.tensor, nsplit=pending.nsplit, split_stride=pending.split_stride)
+            ctx.extras.pop("x_copy", None)
+        h = ctx.extras.get("x_copy")
+        if h is None:
+            h = x
+            if ctx.rt.dtype != x.dtype:
+                h = ctx.ws.get("x_copy", tuple(x.shape), ctx.rt.dtype)
+                K.act_rows(x, h, "copy")
+        a = self.mixer.forward(h, ctx, cache)
+        h = self.mixer_norm.forward_post(x, ctx, a, alpha=self.alpha)
+        if self.feed_forward is not None:
+            f = self.feed_forward.forward(h, ctx)
+            h = self.ff_norm.forward_post(x, ctx, f, alpha=self.alpha)
+        if self.side is not None:
+            h = self.side.forward_into(x, h, ctx)
+        ctx.extras["x_copy"] = h
+        return None

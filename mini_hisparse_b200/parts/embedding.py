@@ -11,24 +11,53 @@ from .spec import ParamSpec, PartSpec
 
 @EMBEDDINGS.register("token_embedding")
 class TokenEmbedding(Part):
-    """x = table[tokens], no scaling (mini_hisparse/model.py:86,166); output is the float32 residual."""
+    """x = table[tokens] (mini_hisparse/model.py:86,166), times ``scale`` if the spec gives one (the
+    reference has none); output is the float32 residual.  ``weight_name``: the tensor's local name
+    ("" if the prefix alone names it).  With ``copy`` the rows are also left in the compute dtype as
+    ctx.extras["x_copy"], for a first block that reads the stream without normalising it."""
 
     def __init__(self, spec: PartSpec, rt=None):
         super().__init__(spec, rt)
         self.vocab = int(spec["vocab_size"])
         self.width = int(spec["hidden_size"])
+        self.scale = float(spec.get("scale", 1.0))
+        self.copy = bool(spec.get("copy", False))
+        self.weight_name = spec.get("weight_name", "weight")
         self.weight = None
 
     def parameters(self):
-        return {"weight": ParamSpec((self.vocab, self.width))}
+        return {self.weight_name: ParamSpec((self.vocab, self.width))}
 
     def load(self, tensors):
-        self.weight = tensors["weight"].contiguous()
+        self.weight = tensors[self.weight_name].contiguous()
 
     def forward(self, ctx: StepContext) -> torch.Tensor:
         x = ctx.ws.get("residual", (ctx.T, self.width), torch.float32)
-        K.embed(self.weight, ctx.tokens, x, status=ctx.status)
+        copy = None
+        if self.copy and ctx.rt.dtype != torch.float32:
+            copy = ctx.ws.get("x_copy", (ctx.T, self.width), ctx.rt.dtype)
+        K.embed(self.weight, ctx.tokens, x, status=ctx.status, scale=self.scale, copy=copy)
+        if self.copy:
+            ctx.extras["x_copy"] = x if copy is None else copy
         return x
+
+
+@EMBEDDINGS.register("token_table")
+class TokenTable(Part):
+    """A table [vocab, width] that other parts index by token id (a model-level part: ModelSpec.shared)."""
+
+    def __init__(self, spec: PartSpec, rt=None):
+        super().__init__(spec, rt)
+        self.vocab = int(spec["vocab_size"])
+        self.width = int(spec["width"])
+        self.weight_name = spec.get("weight_name", "weight")
+        self.weight = None
+
+    def parameters(self):
+        return {self.weight_name: ParamSpec((self.vocab, self.width))}
+
+    def load(self, tensors):
+        self.weight = tensors[self.weight_name].contiguous()
 
 
 @HEADS.register("lm_head")
@@ -41,16 +70,17 @@ class LMHead(Part):
         self.vocab = int(spec["vocab_size"])
         self.width = int(spec["hidden_size"])
         self.tied = bool(spec["tied"])
+        self.weight_name = spec.get("weight_name", "weight")
         self.weight = None
 
     def parameters(self):
         if self.tied:
-            return {"weight": ParamSpec((self.vocab, self.width), optional=True)}
-        return {"weight": ParamSpec((self.vocab, self.width))}
+            return {self.weight_name: ParamSpec((self.vocab, self.width), optional=True)}
+        return {self.weight_name: ParamSpec((self.vocab, self.width))}
 
     def load(self, tensors):
         if not self.tied:
-            self.weight = tensors["weight"].contiguous()
+            self.weight = tensors[self.weight_name].contiguous()
 
     def tie(self, embedding: TokenEmbedding):
         self.weight = embedding.weight

@@ -41,3 +41,86 @@ class SwiGLU(FeedForward):
         rt, ws = ctx.rt, ctx.ws
         act = rt.linear_swiglu(h, self.gate_up, self.gate_block, ws, "ff_act")
         return rt.linear(act, self.down, ws, "ff_out")
+
+
+@register_feed_forward("mlp_act")
+class ActivatedMLP(FeedForward):
+    """down(act(up(x))), no gate, no biases; ``activation``: "relu2" (the square of relu), "silu" or
+    "gelu_tanh", computed in float32 on the product's float32 output.  Tensor names: ``up_name`` and
+    ``down_name`` (default "up" and "down")."""
+
+    def __init__(self, spec: PartSpec, rt=None):
+        super().__init__(spec, rt)
+        self.hidden = int(spec["hidden_size"])
+        self.inter = int(spec["intermediate_size"])
+        self.activation = spec.get("activation", "relu2")
+        if self.activation not in K.ACTIVATIONS or self.activation == "copy":
+            raise ValueError(f"unknown activation {self.activation!r}")
+        self.up_name, self.down_name = spec.get("up_name", "up"), spec.get("down_name", "down")
+        self.up = self.down = None
+
+    def parameters(self):
+        return {self.up_name: ParamSpec((self.inter, self.hidden)),
+                self.down_name: ParamSpec((self.hidden, self.inter))}
+
+    def load(self, tensors):
+        self.up = tensors[self.up_name].contiguous()
+        self.down = tensors[self.down_name].contiguous()
+
+    def forward(self, h, ctx: StepContext) -> Product:
+        rt, ws = ctx.rt, ctx.ws
+        z = rt.linear(h, self.up, ws, "ff_up", out_dtype=torch.float32)
+        act = ws.get("ff_act", (h.shape[0], self.inter), rt.dtype)
+        K.act_rows(z.tensor, act, self.activation, nsplit=z.nsplit, split_stride=z.split_stride)
+        return rt.linear(act, self.down, ws, "ff_out")
+
+
+@register_feed_forward("token_side")
+class TokenSide(FeedForward):
+    """A per-layer input from the token itself, added to the stream as a normalised branch:
+
+        e = table[token, column0 : column0 + dim];  g = gelu_tanh(W_gate x) * e;  y = W_proj g;
+        x <- x + rms(y) * w
+
+    The table is a part of the model (ModelSpec.shared, key ``table``) of which every layer reads its
+    own ``dim`` columns from ``column0``.  Tensors: gate [dim, hidden], proj [hidden, dim], norm [hidden].
+    """
+
+    def __init__(self, spec: PartSpec, rt=None):
+        super().__init__(spec, rt)
+        self.hidden = int(spec["hidden_size"])
+        self.dim = int(spec["dim"])
+        self.column0 = int(spec["column0"])
+        self.eps = float(spec["eps"])
+        self.table_key = spec.get("table", "side")
+        self.table = None
+        self.gate = self.proj = self.norm = None
+
+    def parameters(self):
+        return {"gate": ParamSpec((self.dim, self.hidden)), "proj": ParamSpec((self.hidden, self.dim)),
+                "norm": ParamSpec((self.hidden,), role="vector", init=("normal", 1.0, 0.1))}
+
+    def load(self, tensors):
+        self.gate, self.proj, self.norm = tensors["gate"].contiguous(), tensors["proj"].contiguous(), tensors["norm"]
+
+    def bind(self, shared):
+        self.table = shared[self.table_key]
+        if self.column0 + self.dim > self.table.width:
+            raise ValueError(f"columns {self.column0}..{self.column0 + self.dim} are outside a table {self.table.width} wide")
+
+    def forward_into(self, x, h, ctx: StepContext):
+        """Add the branch into the float32 stream ``x`` (``h``: its rows in the compute dtype); returns
+        the new rows in the compute dtype."""
+        rt, ws = ctx.rt, ctx.ws
+        z = rt.linear(h, self.gate, ws, "side_gate", out_dtype=torch.float32)
+        g = ws.get("side_g", (h.shape[0], self.dim), rt.dtype)
+        K.table_gate(z.tensor, self.table.weight, self.column0, ctx.tokens, g, nsplit=z.nsplit,
+                     split_stride=z.split_stride, status=ctx.status)
+        y = rt.linear(g, self.proj, ws, "side_out", out_dtype=torch.float32)
+        copy = None if rt.dtype == torch.float32 else ws.get("x_copy", tuple(x.shape), rt.dtype)
+        K.norm_mix(x, self.norm, self.eps, delta=y.tensor, nsplit=y.nsplit, split_stride=y.split_stride,
+                   alpha=0.0, keep=1.0, copy=copy)
+        return x if copy is None else copy
+
+    def forward(self, h, ctx):
+        raise NotImplementedError("a token_side part adds into the stream: call forward_into")

@@ -22,13 +22,27 @@ class RMSNorm(Norm):
         super().__init__(spec, rt)
         self.width = int(spec["width"])
         self.eps = float(spec["eps"])
+        self.weight_name = spec.get("weight_name", "weight")     # "" if the tensor is named by the prefix alone
         self.weight = None
 
     def parameters(self):
-        return {"weight": ParamSpec((self.width,), role="vector", init=("normal", 1.0, 0.1))}
+        return {self.weight_name: ParamSpec((self.width,), role="vector", init=("normal", 1.0, 0.1))}
 
     def load(self, tensors):
-        self.weight = tensors["weight"]
+        self.weight = tensors[self.weight_name]
+
+    def forward_post(self, x, ctx: StepContext, delta: Product | None, alpha: float = 1.0, keep: float = 0.0,
+                     name="x_copy"):
+        """Norm AFTER the sum, in place: x <- keep * x + rms(alpha * x + delta) * weight (float32).
+        Returns the new rows in the compute dtype (x itself when that is float32): what the next
+        product reads, since nothing normalises the stream again before it."""
+        copy = None if ctx.rt.dtype == torch.float32 else ctx.ws.get(name, tuple(x.shape), ctx.rt.dtype)
+        if delta is None:
+            K.norm_mix(x, self.weight, self.eps, alpha=alpha, keep=keep, copy=copy)
+        else:
+            K.norm_mix(x, self.weight, self.eps, delta=delta.tensor, nsplit=delta.nsplit,
+                       split_stride=delta.split_stride, alpha=alpha, keep=keep, copy=copy)
+        return x if copy is None else copy
 
     def forward(self, x, ctx: StepContext, delta: Product | None = None, rows=None, name="h"):
         R = x.shape[0] if rows is None else rows.shape[0]

@@ -69,11 +69,19 @@ class LayerSpec:
     block: str
     parts: tuple[tuple[str, PartSpec], ...]
     names: tuple[tuple[str, str], ...] = ()
+    options: tuple[tuple[str, Any], ...] = ()     # constants of the arrangement itself (a residual scale, ...)
 
     @staticmethod
     def make(prefix: str, block: str, parts: Mapping[str, PartSpec],
-             names: Mapping[str, str] | None = None) -> "LayerSpec":
-        return LayerSpec(prefix, block, tuple(parts.items()), tuple((names or {}).items()))
+             names: Mapping[str, str] | None = None, options: Mapping[str, Any] | None = None) -> "LayerSpec":
+        return LayerSpec(prefix, block, tuple(parts.items()), tuple((names or {}).items()),
+                         tuple(sorted((options or {}).items())))
+
+    def option(self, key: str, default=None):
+        return dict(self.options).get(key, default)
+
+    def has(self, role: str) -> bool:
+        return any(r == role for r, _ in self.parts)
 
     @staticmethod
     def pre_norm(prefix: str, *, mixer: PartSpec, mixer_norm: PartSpec, feed_forward: PartSpec,
@@ -126,6 +134,9 @@ class ModelSpec:
     head_name: str
     max_positions: int | None = None
     eos_token_id: int | None = None
+    # parts that belong to the model and not to one layer (a table that every layer reads a slice of):
+    # (key, part of the embeddings' registry, checkpoint prefix); blocks get them through Block.bind()
+    shared: tuple[tuple[str, PartSpec, str], ...] = ()
 
     def __post_init__(self):
         for i, e in enumerate(self.order):
@@ -136,6 +147,12 @@ class ModelSpec:
                     raise ValueError(f"run entry {i} reads the cache of entry {e.cache_of}, which is not earlier")
                 if self.order[e.cache_of].cache_of is not None:
                     raise ValueError(f"run entry {i} reads entry {e.cache_of}, which owns no cache")
+
+
+def join_name(*pieces: str) -> str:
+    """A tensor's name in the checkpoint from its prefix, sub-prefix and local name; empty pieces are
+    left out (a part whose only tensor IS the prefix has the local name "")."""
+    return ".".join(p for p in pieces if p)
 
 
 # ---- what a mixer needs from the cache manager ---------------------------------------------
@@ -166,14 +183,23 @@ class PagedNeed(CacheNeed):
 
 @dataclass(frozen=True)
 class PagedKVNeed(PagedNeed):
-    """Keys and values of every cached position: a page is [2 (K, V), kv_heads, page_size, head_dim]."""
+    """Keys and values of every cached position: a page is [2 (K, V), kv_heads, page_size, head_dim].
+    With values of another width (``v_dim``) a page is flat: the keys [kv_heads, page_size, head_dim]
+    followed by the values [kv_heads, page_size, v_dim], which for equal widths is the same memory."""
 
     kv_heads: int = 1
     head_dim: int = 16
     window: int | None = None
+    v_dim: int | None = None
+
+    def __post_init__(self):
+        if self.v_dim == self.head_dim:          # one way to say it, so that equal needs compare equal
+            object.__setattr__(self, "v_dim", None)
 
     def page_shape(self, page_size: int) -> tuple[int, ...]:
-        return (2, self.kv_heads, page_size, self.head_dim)
+        if self.v_dim is None:
+            return (2, self.kv_heads, page_size, self.head_dim)
+        return (self.kv_heads * page_size * (self.head_dim + self.v_dim),)
 
 
 @dataclass(frozen=True)

@@ -38,7 +38,8 @@ def main() -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens that live requests hold at any time (rounded up per request)")
     ap.add_argument("--page-size", type=int, default=16)
-    ap.add_argument("--max-requests", type=int, default=8)
+    ap.add_argument("--max-requests", type=int, default=4,
+                    help="state slots: the most requests that are live at any time")
     ap.add_argument("--device", default="cuda:0")
     ap.add_argument("--no-graphs", dest="graphs", action="store_false",
                     help="launch decode steps eagerly instead of replaying a captured CUDA graph")

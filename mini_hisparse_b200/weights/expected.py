@@ -2,7 +2,7 @@
 from __future__ import annotations
 
 from ..parts.registry import BLOCKS, EMBEDDINGS, HEADS, NORMS
-from ..parts.spec import ModelSpec, ParamSpec
+from ..parts.spec import ModelSpec, ParamSpec, join_name
 
 
 def expected_tensors_of_spec(spec: ModelSpec) -> dict[str, ParamSpec]:
@@ -10,13 +10,15 @@ def expected_tensors_of_spec(spec: ModelSpec) -> dict[str, ParamSpec]:
 
     def add(prefix, part):
         for local, ps in part.parameters().items():
-            out[f"{prefix}.{local}"] = ps
+            out[join_name(prefix, local)] = ps
 
     add(spec.embedding_name, EMBEDDINGS.build(spec.embedding, rt=None))
+    for _, part, prefix in spec.shared:
+        add(prefix, EMBEDDINGS.build(part, rt=None))
     for layer in spec.layers:
         block = BLOCKS.get(layer.block)(layer, None)
         for role, part in block.parts().items():
-            add(f"{layer.prefix}.{layer.name_of(role)}", part)
+            add(join_name(layer.prefix, layer.name_of(role)), part)
     add(spec.final_norm_name, NORMS.build(spec.final_norm, rt=None))
     add(spec.head_name, HEADS.build(spec.head, rt=None))
     return out

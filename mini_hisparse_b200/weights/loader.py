@@ -17,6 +17,7 @@ from pathlib import Path
 
 import torch
 
+from ..parts.spec import join_name
 from .safetensors_io import Checkpoint, write_safetensors
 
 
@@ -58,7 +59,7 @@ def _deliver(model, fetch) -> None:
     for prefix, part in model.named_parts():
         tensors = {}
         for local, ps in part.parameters().items():
-            t = fetch(f"{prefix}.{local}", ps)
+            t = fetch(join_name(prefix, local), ps)
             if t is not None:
                 tensors[local] = t.to(device=rt.device, dtype=_target_dtype(ps.role, rt.dtype))
         part.load(tensors)

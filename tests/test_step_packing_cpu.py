@@ -63,8 +63,9 @@ def test_packing_with_several_groups_and_planners():
     batch = BatchBuilder(cache, "cpu", sm_count=8)
     users = [batch.add_user(0, a4), batch.add_user(1, a8), batch.add_user(0, a4), batch.add_user(2, MadeUpMixer("m")),
              batch.add_user(3, MadeUpMixer("m")), batch.add_user(4, None)]
-    # plans: one per (group, plan key): a4 (twice the same), a8, the made-up one; the state entry and None plan nothing
-    assert len(batch.slots) == 3 and [batch.users[u][1] for u in users] == [0, 1, 0, 2, None, None]
+    # plans: one per (group, plan key): a4 (twice the same), a8, the made-up one over pages, and the made-up
+    # one over the state group (a state's user may plan too: its group is another one); None plans nothing
+    assert len(batch.slots) == 4 and [batch.users[u][1] for u in users] == [0, 1, 0, 2, 3, None]
     for name in ("x", "y"):
         cache.open(name)
     cache.ensure("x", 9), cache.advance("x", 9)
@@ -92,7 +93,9 @@ def test_packing_with_several_groups_and_planners():
     assert vm.meta["seg_first"].tolist() == [9, 0] and vm.meta["count"] == 2
     assert vm.meta["tok_index"].tolist() == list(range(9)) + [0, 0, 0]      # the rest of its capacity is zeroed
     assert vm.storage is None and vm.page_size == 4
-    assert batch.cache_view(users[4], views).meta == {} and batch.cache_view(users[5], views) is None
+    vs = batch.cache_view(users[4], views)
+    assert vs.meta["seg_first"].tolist() == [9, 0] and vs.meta["count"] == 2 and "block_table" not in vs.meta
+    assert batch.cache_view(users[5], views) is None
 
 
 def test_a_plan_larger_than_its_capacity_is_refused():
