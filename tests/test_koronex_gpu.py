@@ -1,0 +1,455 @@
+"""Koronex through the engine against the plain implementation of tests/plain/koronex_plain.py.
+
+Small configurations made here (none is anyone's model), random weights from a seed.  Covered: the
+kernels of each mechanism alone; whole prompts; prefill against token-by-token decoding (through
+captured graphs); portions down to two tokens; mixed batches over a tight pool whose freed pages are
+poisoned; slots used again; windows' edges, far keys and the sink with inputs made so that one score
+stands out; sizes that are equal or 1; generation through Engine and its scheduler; bin/trace_run.
+"""
+import json
+import math
+
+import pytest
+import torch
+
+import schedules as S
+from conftest import TraceRun, random_tokens, row_rms_error
+from plain import koronex_plain as P
+
+pytestmark = pytest.mark.gpu
+
+
+def attn(heads, kv_heads, dim, vdim, window, rot, base=3000.0, scale=0.3, kv_from=None):
+    m = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, mask=dict(size=window),
+             rot=dict(dims=rot, base=base), scale=scale)
+    if kv_from is not None:
+        m["kv_from"] = kv_from
+    return m
+
+
+def light(heads, dim, vdim, decay):
+    return dict(heads=heads, dim=dim, vdim=vdim, decay=decay)
+
+
+def layer(kind, mixer, ff=None):
+    return dict(type=kind, mixer=mixer, mlp=None if ff is None else dict(kind="dense", ff=ff))
+
+
+# A: every branch at once: attention first, a reader of its keys with a SMALLER window, two lightning
+# layers of different shapes, an attention layer whose window is longer than any test sequence and
+# that rotates whole heads, layers with and without a feed-forward.
+CFG_A = dict(architecture="Koronex", vocab=211, width=96, embedding=dict(scale=2.0), norm=dict(eps=1e-5),
+             postln_alpha=1.7, token_side=dict(dim=8), layers=[
+                 layer("attention", attn(6, 2, 32, 48, 37, 8), ff=160),
+                 layer("lightning", light(3, 16, 24, [0.5, 0.9, 0.995]), ff=64),
+                 layer("attention", attn(6, 2, 32, 48, 21, 8, kv_from=0)),
+                 layer("lightning", light(2, 24, 16, [0.97, 1.0])),
+                 layer("attention", attn(4, 4, 16, 16, 500, 16, base=100.0, scale=0.5), ff=72)])
+# B: values that the usual model makes different are equal or 1 here: one head, as many KV heads as
+# heads, values as wide as keys, a window of one key, no rotation, no token input, a reader whose window
+# is LARGER than its owner's, a width that no tensor-core product takes (not a multiple of 8).
+CFG_B = dict(architecture="Koronex", vocab=97, width=100, embedding=dict(scale=1.0), norm=dict(eps=1e-3),
+             postln_alpha=1.0, layers=[
+                 layer("lightning", light(1, 20, 20, [0.8]), ff=40),
+                 layer("attention", attn(1, 1, 24, 24, 1, 0, scale=1.0)),
+                 layer("attention", attn(3, 3, 16, 16, 9, 0, scale=0.7), ff=50),
+                 layer("attention", attn(3, 3, 16, 16, 33, 0, scale=0.7, kv_from=2))])
+# C: head sizes of a real model's order (64 / 128 wide), many heads per group.
+CFG_C = dict(architecture="Koronex", vocab=300, width=256, embedding=dict(scale=4.0), norm=dict(eps=1e-6),
+             postln_alpha=3.0, token_side=dict(dim=32), layers=[
+                 layer("lightning", light(2, 64, 128, [0.9, 0.99]), ff=512),
+                 layer("attention", attn(8, 1, 64, 128, 70, 32, base=1e6, scale=0.125), ff=384)])
+CONFIGS = {"A": CFG_A, "B": CFG_B, "C": CFG_C}
+# A row's error: the root mean square of (got - plain) as a share of the row's root mean square.  float32:
+# every row within rounding of another summation order; this is the sharp comparison (a window one key off
+# moves a row by 50 times as much: see the sensitivity test).  bfloat16: rounding of the stream and of the
+# activations is amplified by peaked softmaxes and has a heavy tail over rows (a plain model that only
+# rounds the sublayers' inputs to bfloat16 shows a mean of 0.005 and a worst row of 0.03 to 0.1 on these
+# shapes), so the mean over rows is held tightly and the worst row loosely: this comparison catches what is
+# grossly wrong in the bfloat16 path (a stale page, a lost state: errors near 1), and the kernels' own
+# tests above are sharp in both dtypes.
+BF16_MEAN, BF16_WORST = 0.03, 0.3
+F32_ROW = 2e-5
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    from mini_hisparse_b200 import write_random_model
+
+    out = {}
+    for name, cfg in CONFIGS.items():
+        folder = tmp_path_factory.mktemp(f"koronex{name}")
+        write_random_model(cfg, 23, folder, dtype=torch.bfloat16, matrix_std=0.15)
+        out[name] = (folder, *P.load_folder(folder))
+    return out
+
+
+def requests_for(cfg, lengths, seed=0):
+    return {f"r{i}": random_tokens(cfg["vocab"], n, seed + i) for i, n in enumerate(lengths)}
+
+
+def run_steps(folder, dtype, steps, page_size=16, max_requests=4, graphs=True, round_to=64):
+    """Replay ``steps`` through the step function over a pool sized like the replay program's, with
+    poison on freed pages; returns {request: logits of all its positions}."""
+    from mini_hisparse_b200 import CacheConfig, CacheManager, load_model
+    from mini_hisparse_b200.engine import ModelRunner, StepEntry
+
+    model = load_model(folder, dtype=dtype)
+    unit = max(round_to, page_size)
+    pages = -(-S.peak_tokens(steps, unit) // page_size)
+    cache = CacheManager(model.cache_needs, CacheConfig(num_pages=pages, page_size=page_size, max_requests=max_requests,
+                                                        dtype=model.rt.dtype, debug_poison=True))
+    runner = ModelRunner(model, cache, use_graphs=graphs)
+    got = {}
+    for entries, end in steps:
+        for e in entries:
+            if e["id"] not in cache.requests:
+                cache.open(e["id"])
+        logits = runner.step([StepEntry(e["id"], e["tokens"], e["want"]) for e in entries]).cpu()
+        runner.check_status()
+        row = 0
+        for e in entries:
+            got.setdefault(e["id"], []).append(logits[row: row + len(e["want"])].clone())
+            row += len(e["want"])
+        for rid in end:
+            cache.close(rid)
+    cache.assert_invariants()
+    return {k: torch.cat(v) for k, v in got.items()}, runner, cache
+
+
+def check_against_plain(got, refs, dtype, name=None):
+    for rid, ref in refs.items():
+        assert got[rid].shape == ref.shape
+        err = (got[rid].double() - ref.double()).pow(2).mean(-1).sqrt() / ref.double().pow(2).mean(-1).sqrt()
+        if dtype == "float32":
+            assert float(err.max()) < F32_ROW, f"{rid}: row error {float(err.max()):.3g} at {int(err.argmax())}"
+        else:
+            assert float(err.mean()) < BF16_MEAN and float(err.max()) < BF16_WORST, \
+                f"{rid}: mean row error {float(err.mean()):.3g}, worst {float(err.max()):.3g} at {int(err.argmax())}"
+
+
+# ---- the kernels of each mechanism alone --------------------------------------------------------------
+@pytest.mark.parametrize("nsplit", [1, 3])
+def test_norm_after_the_sum_and_normalised_branch(nsplit):
+    from mini_hisparse_b200.kernels import api as K
+
+    g = torch.Generator().manual_seed(1)
+    T, H = 7, 100
+    x = torch.randn(T, H, generator=g)
+    parts = torch.randn(nsplit, T, H, generator=g)
+    w = 1 + 0.1 * torch.randn(H, generator=g)
+    for alpha, keep in ((2.5, 0.0), (0.0, 1.0), (1.0, 0.0)):
+        xd, copy = x.cuda().clone(), torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
+        d = parts.cuda() if nsplit > 1 else parts[0].cuda()
+        K.norm_mix(xd, w.cuda(), 1e-5, delta=d, nsplit=nsplit, split_stride=T * H if nsplit > 1 else 0,
+                   alpha=alpha, keep=keep, copy=copy)
+        s = alpha * x.double() + parts.double().sum(0)
+        ref = keep * x.double() + P.rms(s, 1e-5) * w.double()
+        torch.testing.assert_close(xd.cpu().double(), ref, atol=2e-6, rtol=2e-6)
+        torch.testing.assert_close(copy.cpu().float(), xd.cpu().bfloat16().float(), atol=0, rtol=0)
+
+
+def test_activations_and_table_gate():
+    from mini_hisparse_b200.kernels import api as K
+
+    g = torch.Generator().manual_seed(2)
+    z = 2 * torch.randn(5, 33, generator=g)
+    out = torch.empty(5, 33, device="cuda")
+    K.act_rows(z.cuda(), out, "relu2")
+    torch.testing.assert_close(out.cpu(), torch.relu(z) ** 2, atol=1e-6, rtol=1e-6)
+    table = torch.randn(11, 40, generator=g)
+    tokens = torch.tensor([3, 10, 0, 3, 7], dtype=torch.int32)
+    o2 = torch.empty(5, 8, device="cuda")
+    K.table_gate(z[:, :8].contiguous().cuda(), table.cuda(), 24, tokens.cuda(), o2)
+    ref = P.gelu_tanh(z[:, :8].double()) * table[tokens.long(), 24:32].double()
+    torch.testing.assert_close(o2.cpu().double(), ref, atol=1e-6, rtol=1e-5)
+
+
+def plain_lightning(q, k, v, lam, S0):
+    """o_t = S_t^T q_t with S_t = lam S_(t-1) + k_t v_t^T, for one head; returns (o, S)."""
+    S, out = S0.clone(), []
+    for t in range(q.shape[0]):
+        S = lam * S + torch.outer(k[t], v[t])
+        out.append(S.T @ q[t])
+    return torch.stack(out), S
+
+
+@pytest.mark.parametrize("dk,dv,heads", [(16, 24, 3), (64, 128, 2), (20, 20, 1)])
+def test_lightning_token_by_token_in_chunks_and_plain_agree(dk, dv, heads):
+    """Three segments of unequal length (one of them a single token, one that goes on from a state that
+    is not zero) through the scan and through the chunked route; decays from tiny to one."""
+    from mini_hisparse_b200.kernels import api as K
+    from mini_hisparse_b200.parts.base import Segment
+    from mini_hisparse_b200.parts.lightning import ChunkPlanner
+
+    g = torch.Generator().manual_seed(3)
+    counts, starts, slots = [150, 1, 67], [0, 40, 9], [2, 0, 1]
+    T = sum(counts)
+    decay = torch.tensor([0.05, 1.0, 0.9][:heads])
+    ld = heads * (2 * dk + dv) + 5
+    proj = torch.randn(2, T, ld, generator=g)          # two split-K parts
+    state0 = torch.randn(3, heads, dk, dv, generator=g)
+    segs, tok_seg, pos, off = [], [], [], 0
+    for i, (n, st, sl) in enumerate(zip(counts, starts, slots)):
+        segs.append(Segment(i, sl, st, n, off))
+        tok_seg += [i] * n
+        pos += list(range(st, st + n))
+        off += n
+    dev = lambda a: torch.tensor(a, dtype=torch.int32, device="cuda")
+    z = P.silu(proj.double().sum(0))
+    refs, ref_state = torch.zeros(T, heads * dv, dtype=torch.float64), state0.double().clone()
+    for sg in segs:
+        rows = slice(sg.offset, sg.offset + sg.count)
+        for h in range(heads):
+            S0 = torch.zeros(dk, dv, dtype=torch.float64) if sg.start == 0 else state0[sg.slot, h].double()
+            o, Sn = plain_lightning(z[rows, h * dk:(h + 1) * dk], z[rows, heads * dk + h * dk: heads * dk + (h + 1) * dk],
+                                    z[rows, 2 * heads * dk + h * dv: 2 * heads * dk + (h + 1) * dv], float(decay[h]), S0)
+            refs[rows, h * dv:(h + 1) * dv] = o
+            ref_state[sg.slot, h] = Sn
+    args = lambda st, out: (proj.cuda(), 0, heads * dk, 2 * heads * dk, decay.cuda(), st, out, dev(tok_seg), dev(slots), dev(pos))
+    common = dict(heads=heads, dk=dk, dv=dv, nsplit=2, split_stride=T * ld)
+    # all by the scan
+    st1, o1 = state0.cuda().clone(), torch.zeros(T, heads * dv, device="cuda")
+    K.lightning_scan(*args(st1, o1), **common)
+    # long segments in chunks, the single token by the scan
+    st2, o2 = state0.cuda().clone(), torch.zeros(T, heads * dv, device="cuda")
+    planner = ChunkPlanner(32)
+    arrays, facts = planner.plan(segs, T)
+    assert facts["num_long"] == 2 and facts["num_chunks"] == 5 + 3
+    K.lightning_scan(*args(st2, o2), **common, max_tokens=16)
+    scratch = torch.empty(facts["num_chunks"] * heads * dk * dv, device="cuda")
+    K.lightning_chunked(*args(st2, o2), torch.from_numpy(arrays["chunks"]).cuda(), facts["num_chunks"],
+                        torch.from_numpy(arrays["seg_chunks"]).cuda(), facts["num_long"], scratch, 32, **common)
+    scale = float(refs.abs().max())
+    for o, st in ((o1, st1), (o2, st2)):
+        assert float((o.cpu().double() - refs).abs().max()) < 3e-6 * scale
+        assert float((st.cpu().double() - ref_state).abs().max()) < 3e-6 * float(ref_state.abs().max())
+
+
+def plain_sink_attention(q, k, v, qpos, scale, window, sink):
+    """q [R, H, d] at positions qpos against keys k [L, G, d], values v [L, G, dv] at positions 0..L-1."""
+    R, H, _ = q.shape
+    G = k.shape[1]
+    kpos = torch.arange(k.shape[0])
+    diff = qpos[:, None] - kpos[None, :]
+    seen = (diff >= 0) & (diff < window)
+    out = torch.zeros(R, H, v.shape[2], dtype=torch.float64)
+    for h in range(H):
+        s = (q[:, h] @ k[:, h // (H // G)].T) * scale
+        s = s.masked_fill(~seen, -math.inf)
+        m = torch.maximum(s.max(-1).values, sink[h])
+        e = torch.exp(s - m[:, None])
+        out[:, h] = (e / (e.sum(-1) + torch.exp(sink[h] - m))[:, None]) @ v[:, h // (H // G)]
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("page_size,window,dk,dv", [(16, 48, 32, 48), (8, 33, 64, 128), (16, 300, 16, 16)])
+def test_attention_kernels_at_the_windows_edges_with_a_sink(dtype, page_size, window, dk, dv):
+    """Keys go through the norm-rotate-append kernel into shuffled pages; then a prompt portion and single
+    decoded tokens attend.  The key just inside the window and the key just outside it are made to stand out
+    (set along the probing query, so that their scores are 8 and 10), with values of their own: a window that
+    is one off changes the output by far more than the tolerance.  The sink is large for one head, so leaving it
+    out would show as well."""
+    from mini_hisparse_b200.kernels import api as K
+    from mini_hisparse_b200.parts.attention import AttentionShape, plan_attention
+    from mini_hisparse_b200.parts.base import Segment
+
+    g = torch.Generator().manual_seed(4)
+    H, G, L, rdim, eps, scale = 4, 2, 200, 8, 1e-5, 0.4
+    portion = 30                                   # the last `portion` positions are the step's own tokens
+    pages = -(-L // page_size)
+    table = torch.randperm(pages + 3, generator=g)[:pages].to(torch.int32)
+    pool = torch.full((pages + 3, G * page_size * (dk + dv)), 1e30).to(dtype).cuda()
+    qw, kw, vw = H * dk, G * dk, G * dv
+    proj = torch.randn(L, qw + kw + vw + 3, generator=g)
+    qn, kn = 1 + 0.1 * torch.randn(qw, generator=g), 1 + 0.1 * torch.randn(kw, generator=g)
+    sink = torch.tensor([8.0, -1.0, 0.5, 0.0])
+    probe = L - 5                                  # the query whose window's edges are made to stand out
+    inv = torch.tensor([100.0 ** (-2.0 * i / rdim) for i in range(rdim // 2)])
+    pos = torch.arange(L, dtype=torch.int32)
+    # everything goes through the append kernel in two steps: the history, then the portion
+    q_all = torch.empty(L, qw, dtype=dtype, device="cuda")
+    dev_i = lambda t: t.to(torch.int32).cuda()
+    for lo, hi in ((0, L - portion), (L - portion, L)):
+        K.qknorm_rope_append(proj[lo:hi].contiguous().cuda(), qn.cuda(), kn.cuda(), eps, dev_i(pos[lo:hi]),
+                             torch.zeros(hi - lo, dtype=torch.int32, device="cuda"), dev_i(table[None, :]), inv.cuda(),
+                             rdim, q_all[lo:hi], pool, nq=H, nkv=G, dk=dk, dv=dv, page_size=page_size)
+    # the same in plain torch
+    qf = P.rotate((P.rms(proj[:, :qw].double(), eps) * qn.double()).view(L, H, dk), pos, rdim, 100.0)
+    kf = P.rotate((P.rms(proj[:, qw:qw + kw].double(), eps) * kn.double()).view(L, G, dk), pos, rdim, 100.0)
+    vf = proj[:, qw + kw:qw + kw + vw].double().view(L, G, dv)
+    pk = pool.float().cpu().view(pages + 3, -1)[table.long()]
+    got_k = pk[:, :G * page_size * dk].reshape(pages, G, page_size, dk).permute(0, 2, 1, 3).reshape(-1, G, dk)[:L]
+    got_v = pk[:, G * page_size * dk:].reshape(pages, G, page_size, dv).permute(0, 2, 1, 3).reshape(-1, G, dv)[:L]
+    tol = 2e-6 if dtype == torch.float32 else 0.02
+    assert float((got_k.double() - kf).abs().max()) < tol * float(kf.abs().max())
+    assert float((got_v.double() - vf).abs().max()) < tol * float(vf.abs().max())
+    assert float((q_all.float().cpu().double().view(L, H, dk) - qf).abs().max()) < tol * float(qf.abs().max())
+    # make the edges stand out in the CACHE (and in the plain copy): scale the two keys
+    kc, vc = got_k.double().clone(), got_v.double().clone()      # what the cache holds, rounding included
+    qc = q_all.float().cpu().double().view(L, H, dk)
+    inside, outside = probe - window + 1, probe - window
+    for p_, val, score in ((inside, 3.0, 8.0), (outside, -3.0, 10.0)):
+        if p_ >= 0:
+            page, within = int(table[p_ // page_size]), p_ % page_size
+            flat = pool[page].float()
+            for gk in range(G):
+                qd = qc[probe, gk * (H // G)]                     # the group's first head at the probe
+                key = (qd * (score / (scale * float(qd @ qd)))).to(dtype).double()
+                kc[p_, gk], vc[p_, gk] = key, val
+                a = (gk * page_size + within) * dk
+                flat[a:a + dk] = key.float().cuda()
+                b = G * page_size * dk + (gk * page_size + within) * dv
+                flat[b:b + dv] = val
+            pool[page] = flat.to(dtype)
+    right = plain_sink_attention(qc, kc, vc, torch.arange(L), scale, window, sink.double())
+    if inside >= 0:          # the test is sharp: a window one key off, or no sink, is far from right at the probe
+        for wrong in (plain_sink_attention(qc, kc, vc, torch.arange(L), scale, window + 1, sink.double()),
+                      plain_sink_attention(qc, kc, vc, torch.arange(L), scale, window - 1, sink.double()),
+                      plain_sink_attention(qc, kc, vc, torch.arange(L), scale, window, sink.double() - 50)):
+            assert float((wrong[probe] - right[probe]).abs().max()) > 0.2
+    shape = AttentionShape(H, G, window, 16)
+    out = torch.zeros(L, H * dv, dtype=dtype, device="cuda")
+
+    def attend(segments, rows):
+        T = sum(s.count for s in segments)
+        plan = plan_attention(shape, segments, T, sm_count=148)
+        n = plan.n_small + plan.n_big
+        part_acc = torch.empty(max(1, plan.part_rows), H, dv, device="cuda")
+        part_ml = torch.empty(max(1, plan.part_rows), H, 2, device="cuda")
+        o = torch.zeros(T, H * dv, dtype=dtype, device="cuda")
+        tables = dev_i(table[None, :].repeat(len(segments), 1))
+        positions = dev_i(torch.cat([torch.arange(s.start, s.start + s.count) for s in segments]))
+        K.attention_simt(q_all[rows].contiguous(), pool, o, part_acc, part_ml, dev_i(torch.from_numpy(plan.items)), n, n,
+                         positions, tables, dev_i(torch.from_numpy(plan.tok_part_row)), nq=H, nkv=G, d=dk, dv=dv,
+                         page_size=page_size, window=window, scale=scale, sink=sink.cuda())
+        if plan.part_rows:
+            K.attention_combine(part_acc, part_ml, dev_i(torch.from_numpy(plan.tok_part_row)),
+                                dev_i(torch.from_numpy(plan.tok_nsplit)), o, nq=H, d=dv)
+        return o.float().cpu().double().view(T, H, dv)
+
+    bound = 3e-6 if dtype == torch.float32 else 0.02
+    rows = torch.arange(L - portion, L)
+    got = attend([Segment("a", 0, L - portion, portion, 0)], rows)                  # a portion of a prompt
+    assert float((got - right[rows]).abs().max()) < bound * float(right.abs().max())
+    for t in (probe, L - 1, L - portion):                                            # decoded alone
+        got = attend([Segment("a", 0, t, 1, 0)], torch.tensor([t]))
+        assert float((got[0] - right[t]).abs().max()) < bound * float(right.abs().max())
+
+
+# ---- the model through the step function -----------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_every_schedule_agrees_with_the_plain_model(models, name, dtype):
+    """Whole prompts; most of a prompt and then its tail token by token, three requests side by side
+    (captured graphs, the window passes over decoded tokens); portions of changing size down to two
+    tokens; mixed batches with up to four live requests over a pool that holds no more than they need,
+    so that pages and slots are used again (freed pages are poisoned).  Every position is compared."""
+    folder, cfg, w = models[name]
+    reqs = requests_for(cfg, [150, 1, 23, 97, 64, 2, 131])
+    refs = {rid: P.forward(cfg, w, toks).float() for rid, toks in reqs.items()}
+    page = {"A": 16, "B": 8, "C": 32}[name]
+    for steps in (S.whole(reqs), S.tail_one_by_one(reqs, tail=45), S.changing_portions(reqs), S.mixed(reqs, seed=3)):
+        got, runner, cache = run_steps(folder, dtype, steps, page_size=page)
+        check_against_plain(got, refs, dtype, name)
+    assert cache.snapshot()["page_groups"][0]["pages_reused"] > 0
+
+
+def test_the_plain_model_is_sensitive_to_what_the_tests_are_for(models):
+    """A window one key off, a sink left out, a reader that takes its own keys' layer for another, a decay
+    state that is lost: each moves the plain model's logits by far more than the float32 tolerance, so the
+    comparison above would show them."""
+    import copy
+
+    folder, cfg, w = models["A"]
+    toks = random_tokens(cfg["vocab"], 90, 5)
+    right = P.forward(cfg, w, toks)
+    rms = float(right.pow(2).mean().sqrt())
+
+    def moved(cfg2=None, w2=None):
+        return float((P.forward(cfg2 or cfg, w2 or w, toks) - right).pow(2).mean().sqrt()) / rms
+
+    for li, delta in ((0, 1), (0, -1), (2, 1), (2, -1)):
+        c = copy.deepcopy(cfg)
+        c["layers"][li]["mixer"]["mask"]["size"] += delta
+        assert moved(c) > 50 * F32_ROW
+    w2 = dict(w)
+    w2["l0.mix.sink"] = w["l0.mix.sink"] - 30
+    assert moved(w2=w2) > 50 * F32_ROW
+    c = copy.deepcopy(cfg)
+    c["layers"][1]["mixer"]["decay"] = [0.5, 0.9, 0.9]
+    assert moved(c) > 50 * F32_ROW
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_a_slot_used_again(models, dtype):
+    """A short prompt, then 260 tokens one by one (several windows and many pages long, lightning states
+    carried 260 times), two requests side by side; then their slots serve new requests, which must start
+    from zero states."""
+    folder, cfg, w = models["A"]
+    reqs = requests_for(cfg, [270, 265], seed=40)
+    refs = {rid: P.forward(cfg, w, toks).float() for rid, toks in reqs.items()}
+    steps = S.tail_one_by_one(reqs, tail=260, together=2)
+    again = requests_for(cfg, [50, 31], seed=60)
+    again = {f"again_{k}": v for k, v in again.items()}
+    refs.update({rid: P.forward(cfg, w, toks).float() for rid, toks in again.items()})
+    steps += S.changing_portions(again, sizes=(2, 29, 1, 7))
+    got, runner, cache = run_steps(folder, dtype, steps, max_requests=2)
+    check_against_plain(got, refs, dtype, "A")
+    assert runner.stats["graph_steps"] > 200
+
+
+def test_batches_of_unequal_requests_equal_each_alone(models):
+    """float32: a request's logits in a mixed batch equal those it gets alone, to rounding."""
+    folder, cfg, w = models["C"]
+    reqs = requests_for(cfg, [140, 3, 77, 30], seed=9)
+    alone, _, _ = run_steps(folder, "float32", S.whole(reqs), page_size=16)
+    mixed, _, _ = run_steps(folder, "float32", S.mixed(reqs, seed=11, tail=20), page_size=16)
+    for rid in reqs:
+        assert row_rms_error(mixed[rid], alone[rid]) < F32_ROW
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_engine(models, dtype):
+    """Engine.add_request / run: admission, portions under a token budget, decoding, finishing.  float32 tokens
+    equal the plain model's; in bfloat16 every token is the plain model's choice for the engine's own history,
+    or loses to it by less than rounding."""
+    from mini_hisparse_b200 import Engine, load_model
+
+    folder, cfg, w = models["A"]
+    model = load_model(folder, dtype=dtype)
+    engine = Engine(model, num_pages=40, page_size=16, max_requests=3, max_tokens_per_step=48, graph_after=2)
+    prompts = requests_for(cfg, [70, 9, 33], seed=80)
+    for rid, p in prompts.items():
+        engine.add_request(rid, p, max_new_tokens=12)
+    out = engine.run()
+    engine.cache.assert_invariants()
+    for rid, p in prompts.items():
+        assert len(out[rid]) == 12
+        if dtype == "float32":
+            assert out[rid] == P.generate(cfg, w, p, 12)
+        else:
+            seq = list(p)
+            for tok in out[rid]:
+                logits = P.forward(cfg, w, seq)[-1]
+                assert float(logits.max() - logits[tok]) < 0.05 * float(logits.abs().max())
+                seq.append(tok)
+
+
+def test_trace_run_picks_the_model_by_its_config(models, tmp_path):
+    """bin/trace_run on a Koronex folder: the same program, cache and step function as for every model."""
+    folder, cfg, w = models["B"]
+    reqs = requests_for(cfg, [60, 21], seed=90)
+    refs = {rid: P.forward(cfg, w, toks).float() for rid, toks in reqs.items()}
+    steps = S.mixed(reqs, seed=1, tail=10)
+    run = TraceRun(folder, "float32", tmp_path / "out", S.peak_tokens(steps), page_size=16, extra=("--poison",))
+    got = {}
+    for entries, end in steps:
+        logits = run.step(entries, end)
+        row = 0
+        for e in entries:
+            got.setdefault(e["id"], []).append(logits[row: row + len(e["want"])])
+            row += len(e["want"])
+    assert run.close() == 0
+    check_against_plain({k: torch.cat(v) for k, v in got.items()}, refs, "float32", "B")
