@@ -13,6 +13,7 @@ CUDA graph captured for its batch size; only the packed buffer changes between r
 """
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -472,8 +473,16 @@ class ModelRunner:
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
             before = K.launches
-            with torch.cuda.graph(graph):
-                g.logits = self._forward(g.ws, views, segments, B)
+            # no cyclic garbage collection inside the capture: a collector that frees another runner's
+            # graph or pool there makes a CUDA call that is not allowed while capturing, and the capture fails
+            collecting = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph):
+                    g.logits = self._forward(g.ws, views, segments, B)
+            finally:
+                if collecting:
+                    gc.enable()
             g.launches = K.launches - before
             K.launches = before + 0          # the capture launched nothing
             g.graph = graph

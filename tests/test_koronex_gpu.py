@@ -6,6 +6,7 @@ captured graphs); portions down to two tokens; mixed batches over a tight pool w
 poisoned; slots used again; windows' edges, far keys and the sink with inputs made so that one score
 stands out; sizes that are equal or 1; generation through Engine and its scheduler; bin/trace_run.
 """
+import gc
 import json
 import math
 
@@ -64,12 +65,14 @@ CONFIGS = {"A": CFG_A, "B": CFG_B, "C": CFG_C}
 # every row within rounding of another summation order; this is the sharp comparison (a window one key off
 # moves a row by 50 times as much: see the sensitivity test).  bfloat16: rounding of the stream and of the
 # activations is amplified by peaked softmaxes and has a heavy tail over rows (a plain model that only
-# rounds the sublayers' inputs to bfloat16 shows a mean of 0.005 and a worst row of 0.03 to 0.1 on these
-# shapes), so the mean over rows is held tightly and the worst row loosely: this comparison catches what is
-# grossly wrong in the bfloat16 path (a stale page, a lost state: errors near 1), and the kernels' own
-# tests above are sharp in both dtypes.
-BF16_MEAN, BF16_WORST = 0.03, 0.3
+# rounds the sublayers' inputs to bfloat16 shows a mean of 0.005 and worst rows of 0.03 to 0.1 on these
+# shapes, ten times the median at the same rows where the engine's worst are), so the mean over rows is
+# held tightly and the worst row loosely.  What is sharp in bfloat16: every schedule against the WHOLE
+# prompt in the same dtype (the same roundings, so only the order of sums differs), and the kernels' own
+# tests above.
+BF16_MEAN, BF16_WORST = 0.03, 0.6
 F32_ROW = 2e-5
+BF16_CUT = 0.1
 
 
 @pytest.fixture(scope="module")
@@ -114,7 +117,10 @@ def run_steps(folder, dtype, steps, page_size=16, max_requests=4, graphs=True, r
         for rid in end:
             cache.close(rid)
     cache.assert_invariants()
-    return {k: torch.cat(v) for k, v in got.items()}, runner, cache
+    stats, pages = dict(runner.stats), cache.snapshot()
+    del runner, model
+    gc.collect()                 # captured graphs and pools go now, not inside a later runner's capture
+    return {k: torch.cat(v) for k, v in got.items()}, stats, pages
 
 
 def check_against_plain(got, refs, dtype, name=None):
@@ -350,10 +356,15 @@ def test_every_schedule_agrees_with_the_plain_model(models, name, dtype):
     reqs = requests_for(cfg, [150, 1, 23, 97, 64, 2, 131])
     refs = {rid: P.forward(cfg, w, toks).float() for rid, toks in reqs.items()}
     page = {"A": 16, "B": 8, "C": 32}[name]
+    whole = None
     for steps in (S.whole(reqs), S.tail_one_by_one(reqs, tail=45), S.changing_portions(reqs), S.mixed(reqs, seed=3)):
         got, runner, cache = run_steps(folder, dtype, steps, page_size=page)
         check_against_plain(got, refs, dtype, name)
-    assert cache.snapshot()["page_groups"][0]["pages_reused"] > 0
+        whole = whole or got
+        worst = max(row_rms_error(got[rid], whole[rid]) for rid in reqs)
+        print(f"{name} {dtype}: worst row against the whole prompt {worst:.3g}")
+        assert worst < (F32_ROW if dtype == "float32" else BF16_CUT)
+    assert cache["page_groups"][0]["pages_reused"] > 0
 
 
 def test_the_plain_model_is_sensitive_to_what_the_tests_are_for(models):
@@ -397,7 +408,7 @@ def test_long_decoding_and_a_slot_used_again(models, dtype):
     steps += S.changing_portions(again, sizes=(2, 29, 1, 7))
     got, runner, cache = run_steps(folder, dtype, steps, max_requests=2)
     check_against_plain(got, refs, dtype, "A")
-    assert runner.stats["graph_steps"] > 200
+    assert runner["graph_steps"] > 200
 
 
 def test_batches_of_unequal_requests_equal_each_alone(models):
