@@ -16,6 +16,12 @@ runs one of the two serving workloads instead and prints ITS one JSON line: 32 r
 of 128 to 4,096 tokens in portions of 512 beside decoding at the Qwen2.5-14B shape, or 16 requests of
 8,192 prompt tokens plus 512 generated ones at the Qwen2.5-32B shape with the page pool sized from
 free memory; tokens a second, step-time percentiles, roofline fractions, clocks, and the layer count.
+
+    python bench.py --workload koronex [--sizes 2k,4k]
+
+times the Koronex design beside the Qwen2 dense model at equal width, heads, feed-forward width and layer
+count (random weights): prefill of a 2,048-token prompt and decode at batch 8 with 4,096 tokens of context,
+each with its kernels' times, as one JSON line.
 """
 from __future__ import annotations
 
@@ -59,6 +65,18 @@ def workload(args) -> int:
     return 0
 
 
+def compare(args) -> int:
+    from mini_hisparse_b200 import measure
+
+    result = measure.compare_architectures(tuple(args.sizes.split(",")), steps=args.steps, warmup=args.warmup)
+    first = result["sizes"][args.sizes.split(",")[0]]
+    line = {"metric": "Koronex beside Qwen2 at equal size: prefill and decode tokens/s", "unit": "tokens/s",
+            "value": first["koronex"]["decode"]["tokens_per_s"], "n_gpus": 1, "higher_is_better": True,
+            "impl": "ours", "dtype": "bf16", "data": "synthetic: seeded random weights and token ids", **result}
+    print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -70,7 +88,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the 28 of the config")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS), help="run a serving workload instead of the decode bench")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["koronex"],
+                    help="run a serving workload, or the two-architecture comparison, instead of the decode bench")
+    ap.add_argument("--sizes", default="2k,4k", help="with --workload koronex: which sizes to time")
     ap.add_argument("--graph-after", type=int, default=8,
                     help="with --workload: capture a decode graph at the N-th step that asks for it")
     args = ap.parse_args()
@@ -82,6 +102,10 @@ def main() -> int:
     if args.impl == "reference":
         return reference_arm(args)
     args.warmup = max(args.warmup, 3)
+    if args.workload == "koronex":
+        if args.steps == 64:
+            args.steps = 32
+        return compare(args)
     if args.workload:
         return workload(args)
 

@@ -1,0 +1,60 @@
+// The tensor-core attention of attention_mma_kernel.cuh with the options that other mixers bring: keys
+// and values of different widths (any multiples of 8 up to 128; the tiles are padded to the next
+// multiple of 32), a sink per query head in the softmax's denominator, a gate on the output, and
+// softmax weights that keep 16 bits in the value product.  Work items, tile heights and the merge of
+// key splits are those of attention_mma.cu.
+#include "attention_mma_kernel.cuh"
+
+using namespace mhb;
+using namespace mhb_amma;
+
+MHB_EXPORT const char* mhb_last_error() { return error_buffer(); }
+
+namespace {
+template <int D, int ROWS>
+int dispatch_dv(int dvp, const AttnArgs& a, int launch_items, cudaStream_t stream) {
+    switch (dvp) {
+        case 32: return launch<D, 32, ROWS, true>(a, launch_items, stream);
+        case 64: return launch<D, 64, ROWS, true>(a, launch_items, stream);
+        case 96: return launch<D, 96, ROWS, true>(a, launch_items, stream);
+        case 128: return launch<D, 128, ROWS, true>(a, launch_items, stream);
+    }
+    return fail("attention_mma_ext: values %d wide", dvp);
+}
+template <int ROWS>
+int dispatch_d(int dp, int dvp, const AttnArgs& a, int launch_items, cudaStream_t stream) {
+    switch (dp) {
+        case 32: return dispatch_dv<32, ROWS>(dvp, a, launch_items, stream);
+        case 64: return dispatch_dv<64, ROWS>(dvp, a, launch_items, stream);
+        case 96: return dispatch_dv<96, ROWS>(dvp, a, launch_items, stream);
+        case 128: return dispatch_dv<128, ROWS>(dvp, a, launch_items, stream);
+    }
+    return fail("attention_mma_ext: keys %d wide", dp);
+}
+}  // namespace
+
+MHB_EXPORT int mhb_attention_mma_ext_supports(int d, int dv) {
+    return d >= 8 && d <= 128 && d % 8 == 0 && dv >= 8 && dv <= 128 && dv % 8 == 0;
+}
+
+MHB_EXPORT int mhb_attention_mma_ext(const void* q, const void* cache, void* out, float* part_acc,
+                                     float* part_ml, const int* items, int num_items, int launch_items,
+                                     int rows, const int* positions, const int* block_table, int width,
+                                     const int* tok_part_row, const int* tok_nsplit, int* counters, int nq,
+                                     int nkv, int d, int dv, int P, int num_pages, int window, float scale,
+                                     const float* sink, const float* gate, int gate_nsplit,
+                                     long long gate_split_stride, int gate_ld, cudaStream_t stream) {
+    if (launch_items <= 0) return 0;
+    if (nkv <= 0 || nq % nkv) return fail("attention: %d query heads over %d KV heads", nq, nkv);
+    if (!mhb_attention_mma_ext_supports(d, dv)) return fail("attention_mma_ext: widths %d and %d (multiples of 8 up to 128)", d, dv);
+    if (!(scale > 0.f) && sink) return fail("attention_mma_ext: a sink needs a positive scale");
+    AttnArgs a;
+    fill_args(a, q, cache, out, part_acc, part_ml, items, num_items, positions, block_table, width, tok_part_row,
+              tok_nsplit, counters, nq, nkv, P, num_pages, window, scale);
+    a.d = d; a.dv = dv; a.sink = sink; a.gate = gate; a.gate_nsplit = gate_nsplit; a.gate_ld = gate_ld;
+    a.gate_split_stride = (size_t)gate_split_stride;
+    const int dp = (d + 31) / 32 * 32, dvp = (dv + 31) / 32 * 32;
+    if (rows == 64) return dispatch_d<64>(dp, dvp, a, launch_items, stream);
+    if (rows == 16) return dispatch_d<16>(dp, dvp, a, launch_items, stream);
+    return fail("attention_mma_ext: tile height %d", rows);
+}

@@ -477,6 +477,31 @@ def attention_mma(q, cache, out, part_acc, part_ml, items, num_items, rows, posi
         "attention_mma")
 
 
+def attention_mma_ext_supports(d: int, dv: int) -> bool:
+    """Widths of keys and values the tensor-core attention with options takes (tiles padded to multiples of 32)."""
+    return 8 <= d <= 128 and d % 8 == 0 and 8 <= dv <= 128 and dv % 8 == 0
+
+
+def attention_mma_ext(q, cache, out, part_acc, part_ml, items, num_items, rows, positions, block_table,
+                      tok_part_row, *, nq, nkv, d, dv, page_size, window=0, scale=None, tok_nsplit=None,
+                      counters=None, sink=None, gate=None, gate_nsplit=1, gate_split_stride=0):
+    """attention_mma with the options of attention_simt: values ``dv`` wide in pages that hold the keys of
+    all KV heads followed by their values, a ``sink`` per query head, a ``gate`` on the output; the softmax's
+    weights enter the value product as two bfloat16 numbers each (16 bits instead of 8)."""
+    lib = build.load("attention_mma_ext")
+    if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or not cache.is_contiguous():
+        raise KernelError("attention_mma_ext: q and the (contiguous) pool must be bfloat16")
+    if scale is None:
+        scale = float(d) ** -0.5
+    g = _gate_args(gate, gate_nsplit, gate_split_stride)
+    _check(lib, lib.mhb_attention_mma_ext(
+        _ptr(q), _ptr(cache), _ptr(out), _ptr(part_acc), _ptr(part_ml), _ptr(items), c_int(num_items),
+        c_int(num_items), c_int(rows), _ptr(positions), _ptr(block_table), c_int(block_table.shape[-1]),
+        _ptr(tok_part_row), _ptr(tok_nsplit), _ptr(counters), c_int(nq), c_int(nkv), c_int(d), c_int(dv),
+        c_int(page_size), c_int(cache.shape[0]), c_int(window or 0), c_float(scale), _ptr(sink),
+        g[0], g[1], g[2], g[3], _stream()), "attention_mma_ext")
+
+
 def attention_tma_supports(d: int, page_size: int) -> bool:
     """Head sizes and page sizes the TMA-fed attention kernel is built for."""
     return d in (64, 128) and 2 <= page_size <= 64 and 64 % page_size == 0

@@ -382,3 +382,195 @@ def workload_prompts(name: str, vocab: int, seed: int = 0) -> tuple[list[list[in
         raise ValueError(f"unknown workload {name!r}: serving14b or long32b")
     prompts = [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lengths]
     return prompts, settings
+
+
+# ---- two architectures side by side at equal size -------------------------------------------------------
+def koronex_shape(width: int, heads: int, kv_heads: int, head_dim: int, ff: int, layers: int, vocab: int,
+                  window: int = 1024, side_dim: int = 64) -> dict:
+    """A Koronex config.json of a real model's sizes: groups of four layers (lightning attention, two
+    windowed attention layers, a third that reads the second's keys), every layer with a feed-forward."""
+    att = dict(heads=heads, kv_heads=kv_heads, dim=head_dim, vdim=head_dim, mask=dict(size=window),
+               rot=dict(dims=head_dim // 2, base=10000.0), scale=head_dim ** -0.5)
+    out = []
+    for i in range(layers):
+        mlp = dict(kind="dense", ff=ff)
+        if i % 4 == 0:
+            decay = [float(1.0 - 2.0 ** (-(3 + 5 * h / max(1, heads - 1)))) for h in range(heads)]
+            out.append(dict(type="lightning", mixer=dict(heads=heads, dim=head_dim, vdim=head_dim, decay=decay), mlp=mlp))
+        elif i % 4 == 3:
+            out.append(dict(type="attention", mixer=dict(att, kv_from=i - 1), mlp=mlp))
+        else:
+            out.append(dict(type="attention", mixer=dict(att), mlp=mlp))
+    return dict(architecture="Koronex", vocab=vocab, width=width, embedding=dict(scale=1.0), norm=dict(eps=1e-5),
+                postln_alpha=1.0, token_side=dict(dim=side_dim), layers=out)
+
+
+def qwen2_shape(width: int, heads: int, kv_heads: int, head_dim: int, ff: int, layers: int, vocab: int) -> dict:
+    return dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", vocab_size=vocab, hidden_size=width,
+                intermediate_size=ff, num_hidden_layers=layers, num_attention_heads=heads,
+                num_key_value_heads=kv_heads, head_dim=head_dim, rms_norm_eps=1e-6, rope_theta=1e6,
+                tie_word_embeddings=False, max_position_embeddings=32768)
+
+
+class KernelTimes:
+    """Times every launch made through kernels.api inside the block with CUDA events, by function name
+    (eager steps only: a replayed graph makes no calls here)."""
+
+    SKIP = {"stream_scope", "dtype_code", "stream_k_scratch", "gemm_tc_wait_limit", "KernelError",
+            "attention_decode_supports", "attention_tma_supports", "gemm_tc_qkv_rope_supports",
+            "attention_decode_max_clusters", "lightning_chunk_smem"}
+
+    def __enter__(self):
+        self.saved, self.events = {}, []
+        for name, fn in list(vars(K).items()):
+            if callable(fn) and not name.startswith("_") and name not in self.SKIP and getattr(fn, "__module__", "") == K.__name__:
+                self.saved[name] = fn
+                setattr(K, name, self._timed(name, fn))
+        return self
+
+    def _timed(self, name, fn):
+        def call(*a, **kw):
+            if getattr(self, "inside", False):         # a function that calls another: count the outer one
+                return fn(*a, **kw)
+            self.inside = True
+            try:
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record()
+                r = fn(*a, **kw)
+                e.record()
+            finally:
+                self.inside = False
+            shape = tuple(a[0].shape) if a and isinstance(a[0], torch.Tensor) else ()
+            self.events.append((name, shape, s, e))
+            return r
+        return call
+
+    def __exit__(self, *exc):
+        for name, fn in self.saved.items():
+            setattr(K, name, fn)
+        torch.cuda.synchronize()
+        self.by_name: dict[str, float] = {}
+        self.calls: dict[str, int] = {}
+        for name, shape, s, e in self.events:
+            self.by_name[name] = self.by_name.get(name, 0.0) + s.elapsed_time(e) * 1e3
+            self.calls[name] = self.calls.get(name, 0) + 1
+
+    def table(self) -> dict:
+        return {n: {"us": round(t, 1), "calls": self.calls[n]} for n, t in sorted(self.by_name.items(), key=lambda kv: -kv[1])}
+
+
+def architecture_point(config: dict, *, prefill_tokens=2048, batch=8, context=4096, steps=32, warmup=4,
+                       page_size=16, kernels=True) -> dict:
+    """Prefill of one prompt and decode at one batch size for any registered architecture, device-timed
+    through the step function; with ``kernels`` also one eager prefill step and one eager decode step
+    timed launch by launch."""
+    import gc
+
+    from .cache.manager import CacheConfig, CacheManager
+    from .engine.engine import load_model
+    from .engine.step import ModelRunner, StepEntry
+
+    model = load_model(config, device="cuda:0", dtype="bfloat16", random_seed=0)
+    vocab = model.spec.vocab_size
+    g = torch.Generator().manual_seed(5)
+    out = {"weight_bytes": model.weight_bytes()}
+
+    def runner_for(pages, requests, graphs=True):
+        cache = CacheManager(model.cache_needs, CacheConfig(num_pages=pages, page_size=page_size, max_requests=requests,
+                                                            dtype=model.rt.dtype))
+        return ModelRunner(model, cache, use_graphs=graphs), cache
+
+    # prefill
+    runner, cache = runner_for(prefill_tokens // page_size + 8, 2)
+    times = []
+    for i in range(4):
+        cache.open(i)
+        toks = torch.randint(0, vocab, (prefill_tokens,), generator=g).tolist()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        runner.step([StepEntry(i, toks, [prefill_tokens - 1])])
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+        cache.close(i)
+    out["prefill"] = {"tokens": prefill_tokens, "ms": min(times[1:]), "tokens_per_s": prefill_tokens / (min(times[1:]) / 1e3)}
+    if kernels:
+        cache.open("k")
+        toks = torch.randint(0, vocab, (prefill_tokens,), generator=g).tolist()
+        with KernelTimes() as kt:
+            runner.step([StepEntry("k", toks, [prefill_tokens - 1])])
+        out["prefill"]["kernels"] = kt.table()
+        cache.close("k")
+    runner.check_status()
+    del runner, cache
+    gc.collect()
+    torch.cuda.empty_cache()
+    # decode
+    runner, cache = runner_for(batch * (context // page_size + 1), batch)
+    for grp in cache.page_groups:
+        grp.storage.normal_(0.0, 0.5)
+    names = list(range(batch))
+    start_ctx = context - steps - warmup - 2
+    for n in names:
+        cache.open(n)
+        cache.ensure(n, start_ctx)
+        cache.advance(n, start_ctx)
+
+    def entries():
+        toks = torch.randint(0, vocab, (batch,), generator=g).tolist()
+        return [StepEntry(n, [t], [0]) for n, t in zip(names, toks)]
+    for _ in range(warmup):
+        runner.step(entries())
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler() as clocks:
+        a.record()
+        for _ in range(steps):
+            runner.step(entries())
+        b.record()
+        torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / steps
+    # bytes a decode step must read: the weights once, the keys and values that every layer's window
+    # still sees, and every state (read and written)
+    kv = 0
+    for grp in cache.page_groups:
+        seen = context if grp.window is None else min(context, grp.window)
+        kv += grp.page_bytes() // page_size * seen * batch
+    state = sum(2 * grp.storage[:, :batch].numel() * grp.storage.element_size() for grp in cache.state_groups)
+    emb = model.embedding.weight
+    nbytes = model.weight_bytes() - emb.numel() * emb.element_size() + kv + state
+    p = peaks()
+    out["decode"] = {"batch": batch, "context": context, "ms_per_step": ms, "tokens_per_s": batch / (ms / 1e3),
+                     "bytes": nbytes, "gbs": nbytes / (ms / 1e3) / 1e9, "hbm_frac": nbytes / (ms / 1e3) / 1e9 / p["hbm_gbs"],
+                     "graph_steps": runner.stats["graph_steps"], "clocks": clocks.result}
+    if kernels:
+        runner.use_graphs = False
+        with KernelTimes() as kt:
+            runner.step(entries())
+        out["decode"]["kernels"] = kt.table()
+    runner.check_status()
+    del runner, cache, model
+    gc.collect()
+    torch.cuda.empty_cache()
+    return out
+
+
+COMPARE_SIZES = {
+    # name: width, heads, kv_heads, head_dim, ff, layers, vocab
+    "2k": (2048, 16, 4, 128, 8192, 8, 32000),
+    "4k": (4096, 32, 8, 128, 14336, 8, 32000),
+}
+
+
+def compare_architectures(sizes=("2k", "4k"), **kw) -> dict:
+    """Koronex beside the Qwen2 dense model at equal width, heads, feed-forward width and layer count."""
+    out = {"peaks": peaks(), "sizes": {}}
+    for name in sizes:
+        shape = COMPARE_SIZES[name]
+        out["sizes"][name] = {
+            "shape": dict(zip(("width", "heads", "kv_heads", "head_dim", "ff", "layers", "vocab"), shape)),
+            "koronex": architecture_point(koronex_shape(*shape), **kw),
+            "qwen2": architecture_point(qwen2_shape(*shape), **kw),
+        }
+    return out

@@ -268,6 +268,8 @@ class AttentionPlanner(StepPlanner):
         SM), never more, so that no CTA waits for a second wave, and no share shorter than
         MIN_KEYS_PER_SPLIT keys.  Without a cluster kernel: (shares, 1)."""
         ctas = segments_count * self.shape.kv_heads * self.chunks
+        if self.shape.window:            # a token never attends to more keys than its window holds
+            max_positions = min(max_positions, self.shape.window)
         n = max(1, min(MAX_SPLITS, (2 * self.sm_count) // ctas, max_positions // MIN_KEYS_PER_SPLIT))
         if self.clusters_of is None or self.chunks != 1 or n == 1:
             return n, 1

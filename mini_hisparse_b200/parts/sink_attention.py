@@ -52,7 +52,16 @@ class SinkAttention(Mixer):
         self.qw, self.kw, self.vw, self.ow = self.nq * self.dk, self.nkv * self.dk, self.nkv * self.dv, self.nq * self.dv
         self.weight = self.o_weight = self.q_norm = self.k_norm = self.sink = None
 
+    def kernel_family(self) -> str:
+        """"mma": the tensor-core kernel with options (bfloat16, widths that are multiples of 8 up to 128);
+        "simt": the CUDA-core kernel (float32, and every other width)."""
+        if self.rt is not None and self.rt.dtype == torch.bfloat16 and K.attention_mma_ext_supports(self.dk, self.dv):
+            return "mma"
+        return "simt"
+
     def kernel_modules(self):
+        if self.kernel_family() == "mma":
+            return ("attention_simt", "attention_mma_ext", "postnorm")
         return ("attention_simt", "postnorm")
 
     def cache_need(self):
@@ -62,7 +71,8 @@ class SinkAttention(Mixer):
         return ("sink_attention", self.nq, self.nkv, self.window)
 
     def planner(self, page_size: int, sm_count: int):
-        return AttentionPlanner(AttentionShape(self.nq, self.nkv, self.window, ROW_TILE), sm_count)
+        rows = 64 if self.kernel_family() == "mma" else ROW_TILE
+        return AttentionPlanner(AttentionShape(self.nq, self.nkv, self.window, rows), sm_count)
 
     def parameters(self):
         p = {"q": ParamSpec((self.qw, self.hidden)), "g": ParamSpec((self.ow, self.hidden)),
@@ -101,7 +111,21 @@ class SinkAttention(Mixer):
         part_rows = max(1, meta["part_rows_cap"])
         part_acc = ws.get("attn_part_acc", (part_rows, self.nq, self.dv), torch.float32)
         part_ml = ws.get("attn_part_ml", (part_rows, self.nq, 2), torch.float32)
-        n = meta["n_small"] + meta["n_big"]
+        n_small, n_big = meta["n_small"], meta["n_big"]
+        n = n_small + n_big
+        if self.kernel_family() == "mma":
+            args = (q, cache.storage, attn, part_acc, part_ml)
+            tail = (ctx.positions, meta["block_table"], meta["tok_part_row"])
+            common = dict(nq=self.nq, nkv=self.nkv, d=self.dk, dv=self.dv, page_size=cache.page_size,
+                          window=self.window or 0, scale=self.scale, sink=self.sink, **gate)
+            if n_small:          # decoded tokens and short portions: 16-row tiles, key splits merged by the last CTA
+                chunks = -(-(self.nq // self.nkv) // ROW_TILE)
+                counters = ws.get_zeroed("attn_counters", (T * self.nkv * chunks,), torch.int32)
+                K.attention_mma_ext(*args, meta["items"], n_small, 16, *tail, **common,
+                                    tok_nsplit=meta["tok_nsplit"], counters=counters)
+            if n_big:            # long portions: 64-row tiles
+                K.attention_mma_ext(*args, meta["items"][n_small * ITEM_INTS:], n_big, 64, *tail, **common)
+            return rt.linear(attn, self.o_weight, ws, "mix_out")
         if n:
             K.attention_simt(q, cache.storage, attn, part_acc, part_ml, meta["items"], n, n, ctx.positions,
                              meta["block_table"], meta["tok_part_row"], nq=self.nq, nkv=self.nkv, d=self.dk,

@@ -249,9 +249,10 @@ def plain_sink_attention(q, k, v, qpos, scale, window, sink):
     return out
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("page_size,window,dk,dv", [(16, 48, 32, 48), (8, 33, 64, 128), (16, 300, 16, 16)])
-def test_attention_kernels_at_the_windows_edges_with_a_sink(dtype, page_size, window, dk, dv):
+@pytest.mark.parametrize("dtype,kernel", [(torch.float32, "simt"), (torch.bfloat16, "simt"), (torch.bfloat16, "mma")])
+@pytest.mark.parametrize("page_size,window,dk,dv", [(16, 48, 32, 48), (8, 33, 64, 128), (16, 300, 16, 16),
+                                                    (16, 70, 40, 24)])
+def test_attention_kernels_at_the_windows_edges_with_a_sink(dtype, kernel, page_size, window, dk, dv):
     """Keys go through the norm-rotate-append kernel into shuffled pages; then a prompt portion and single
     decoded tokens attend.  The key just inside the window and the key just outside it are made to stand out
     (set along the probing query, so that their scores are 8 and 10), with values of their own: a window that
@@ -315,8 +316,7 @@ def test_attention_kernels_at_the_windows_edges_with_a_sink(dtype, page_size, wi
                       plain_sink_attention(qc, kc, vc, torch.arange(L), scale, window - 1, sink.double()),
                       plain_sink_attention(qc, kc, vc, torch.arange(L), scale, window, sink.double() - 50)):
             assert float((wrong[probe] - right[probe]).abs().max()) > 0.2
-    shape = AttentionShape(H, G, window, 16)
-    out = torch.zeros(L, H * dv, dtype=dtype, device="cuda")
+    shape = AttentionShape(H, G, window, 64 if kernel == "mma" else 16)
 
     def attend(segments, rows):
         T = sum(s.count for s in segments)
@@ -327,9 +327,21 @@ def test_attention_kernels_at_the_windows_edges_with_a_sink(dtype, page_size, wi
         o = torch.zeros(T, H * dv, dtype=dtype, device="cuda")
         tables = dev_i(table[None, :].repeat(len(segments), 1))
         positions = dev_i(torch.cat([torch.arange(s.start, s.start + s.count) for s in segments]))
-        K.attention_simt(q_all[rows].contiguous(), pool, o, part_acc, part_ml, dev_i(torch.from_numpy(plan.items)), n, n,
-                         positions, tables, dev_i(torch.from_numpy(plan.tok_part_row)), nq=H, nkv=G, d=dk, dv=dv,
-                         page_size=page_size, window=window, scale=scale, sink=sink.cuda())
+        items = dev_i(torch.from_numpy(plan.items))
+        common = dict(nq=H, nkv=G, d=dk, dv=dv, page_size=page_size, window=window, scale=scale, sink=sink.cuda())
+        if kernel == "mma":
+            head = (q_all[rows].contiguous(), pool, o, part_acc, part_ml)
+            tail = (positions, tables, dev_i(torch.from_numpy(plan.tok_part_row)))
+            if plan.n_small:
+                counters = torch.zeros(T * G, dtype=torch.int32, device="cuda")
+                K.attention_mma_ext(*head, items, plan.n_small, 16, *tail, **common,
+                                    tok_nsplit=dev_i(torch.from_numpy(plan.tok_nsplit)), counters=counters)
+                assert int(counters.abs().sum()) == 0
+            if plan.n_big:
+                K.attention_mma_ext(*head, items.view(-1)[plan.n_small * 8:], plan.n_big, 64, *tail, **common)
+            return o.float().cpu().double().view(T, H, dv)
+        K.attention_simt(q_all[rows].contiguous(), pool, o, part_acc, part_ml, items, n, n,
+                         positions, tables, dev_i(torch.from_numpy(plan.tok_part_row)), **common)
         if plan.part_rows:
             K.attention_combine(part_acc, part_ml, dev_i(torch.from_numpy(plan.tok_part_row)),
                                 dev_i(torch.from_numpy(plan.tok_nsplit)), o, nq=H, d=dv)
@@ -338,6 +350,9 @@ def test_attention_kernels_at_the_windows_edges_with_a_sink(dtype, page_size, wi
     bound = 3e-6 if dtype == torch.float32 else 0.02
     rows = torch.arange(L - portion, L)
     got = attend([Segment("a", 0, L - portion, portion, 0)], rows)                  # a portion of a prompt
+    assert float((got - right[rows]).abs().max()) < bound * float(right.abs().max())
+    rows = torch.arange(L - 9, L)
+    got = attend([Segment("a", 0, L - 9, 9, 0)], rows)                               # a short portion (16-row tiles)
     assert float((got - right[rows]).abs().max()) < bound * float(right.abs().max())
     for t in (probe, L - 1, L - portion):                                            # decoded alone
         got = attend([Segment("a", 0, t, 1, 0)], torch.tensor([t]))
