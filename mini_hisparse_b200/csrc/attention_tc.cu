@@ -58,7 +58,21 @@ struct AttnArgs {
     int* status;
     int num_items, width, nq, nkv, P, num_pages, window;
     float scale;
+    // the options of a mixer that brings them (EXT instances only): a sink per query head in the softmax's
+    // denominator, and a gate (columns of a float32 product, split-K parts summed in order) on the output
+    const float* sink;
+    const float* gate;
+    int gate_nsplit, gate_ld;
+    size_t gate_split_stride;
 };
+
+__device__ __forceinline__ float gate_of(const AttnArgs& a, int t, int col) {
+    if (!a.gate) return 1.f;
+    const size_t idx = (size_t)t * a.gate_ld + col;
+    float g = a.gate[idx];
+    for (int s = 1; s < a.gate_nsplit; ++s) g += a.gate[idx + (size_t)s * a.gate_split_stride];
+    return 1.f / (1.f + expf(-g));
+}
 
 constexpr int K_STAGES = 3;
 constexpr int V_STAGES = 2;      // value tile j shares its barriers with P(j): both are indexed by j & 1
@@ -86,7 +100,11 @@ __device__ __forceinline__ uint32_t swz_addr(uint32_t base, int rows_per_half, i
     return base + (e >> 6) * rows_per_half * 128 + r * 128 + ((((e & 63) >> 3) ^ (r & 7)) << 4);
 }
 
-template <int D>
+// EXT: the options.  The sink starts a row's reference maximum and sum at (sink / scale, 1), in the unsplit
+// item or in split 0 only.  The softmax's weights enter the value product as two bfloat16 numbers, the weight
+// and what rounding it lost: P(j) keeps the first 32 columns of S(j)'s buffer and the remainders take the
+// other 32, with a second run of MMAs for them (16 bits of the weights instead of 8).
+template <int D, bool EXT>
 __global__ void __launch_bounds__(THREADS, 2)
 attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a) {
     using L = Layout<D>;
@@ -235,6 +253,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
                 for (int k = 0; k < KT / 16; ++k)
                     umma_bf16_tmem_a(tmem + 128, tmem + (j & 1) * KT + k * 8, v_desc + (uint64_t)(k * 16 * 128 / 16), idesc_o,
                                      (j > 0 || k > 0) ? 1u : 0u);
+                if constexpr (EXT) {          // what rounding the weights lost, over the same values
+#pragma unroll
+                    for (int k = 0; k < KT / 16; ++k)
+                        umma_bf16_tmem_a(tmem + 128, tmem + (j & 1) * KT + 32 + k * 8, v_desc + (uint64_t)(k * 16 * 128 / 16),
+                                         idesc_o, 1u);
+                }
                 umma_commit(o_done(j & 1));             // O holds tiles 0..j and V(j) is consumed when this completes
                 if (j + 1 == ntiles) umma_commit(o_final);
                 if (j + 2 < ntiles) issue_s(j + 2);
@@ -268,6 +292,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
         const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
         float m_ref = -INFINITY;      // the maximum the exponentials refer to (at most 2^8 below the true one)
         float l_run = 0.f;
+        if constexpr (EXT) {
+            if (a.sink && live && split <= 0) {      // the sink is not scaled: in the raw products' units it is sink / scale
+                m_ref = a.sink[hq] / a.scale;
+                l_run = 1.f;
+            }
+        }
 
         for (int j = 0; j < ntiles; ++j) {
             ok = mbar_wait(s_full(j & 1), (j >> 1) & 1);
@@ -305,16 +335,23 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
             const float m_scaled = m_use * scale_log2;
             float ps4[4] = {0.f, 0.f, 0.f, 0.f};       // four independent chains again
             uint32_t pw[KT / 2];
+            uint32_t plo[EXT ? KT / 2 : 1];
 #pragma unroll
             for (int x = 0; x < KT; x += 2) {
                 const float p0 = fast_exp2(fmaf(__uint_as_float(sr[x]), scale_log2, -m_scaled));
                 const float p1 = fast_exp2(fmaf(__uint_as_float(sr[x + 1]), scale_log2, -m_scaled));
                 ps4[(x >> 1) & 3] += p0 + p1;
                 pw[x >> 1] = pack_bf16(p0, p1);
+                if constexpr (EXT)
+                    plo[x >> 1] = pack_bf16(p0 - __bfloat162float(__float2bfloat16_rn(p0)),
+                                            p1 - __bfloat162float(__float2bfloat16_rn(p1)));
             }
             const float psum = (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
             const bool rescale = raise && m_old > -INFINITY;     // there is an accumulator to rescale
-            if (__any_sync(0xffffffffu, rescale)) {
+            if (EXT && j == 0) {
+                // only a sink can have set a reference before the first tile: there is a sum to rescale, no accumulator yet
+                if (rescale) l_run *= exp2f((m_old - m_use) * scale_log2);
+            } else if (__any_sync(0xffffffffu, rescale)) {
                 // O is only ours once the previous tile's P V has completed
                 ok = mbar_wait(o_done((j - 1) & 1), ((j - 1) >> 1) & 1);
                 if (!ok) break;
@@ -333,6 +370,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
             }
             // P(j) over the first 32 columns of S(j)'s buffer: column i holds keys 2i and 2i + 1
             tmem_st32(lane_addr + (j & 1) * KT, pw);
+            if constexpr (EXT) tmem_st32(lane_addr + (j & 1) * KT + 32, plo);
             tmem_st_wait();
             l_run += psum;
             tc_fence_before();
@@ -369,6 +407,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
         } else if (ok) {
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             __nv_bfloat16* dst = a.out + ((size_t)t * a.nq + hq) * D;
+            const bool gated = EXT && a.gate != nullptr && live;
 #pragma unroll
             for (int c = 0; c < D; c += 16) {
                 uint32_t r[16];
@@ -378,6 +417,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
                 } else {
 #pragma unroll
                     for (int x = 0; x < 16; ++x) r[x] = 0;
+                }
+                if (gated) {
+#pragma unroll
+                    for (int x = 0; x < 16; ++x) r[x] = __float_as_uint(__uint_as_float(r[x]) * gate_of(a, t, hq * D + c + x));
                 }
                 if (live) {
                     uint4 v0, v1;
@@ -401,9 +444,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
     if (warp == 1) tmem_dealloc(tmem, L::TMEM_COLS);
 }
 
-template <int D>
+template <int D, bool EXT>
 int launch(const CUtensorMap& map, const AttnArgs& a, int launch_items, cudaStream_t stream) {
-    auto kern = attention_tc_kernel<D>;
+    auto kern = attention_tc_kernel<D, EXT>;
     constexpr int smem = Layout<D>::TOTAL;
     static bool configured = false;
     if (!configured) {
@@ -443,5 +486,34 @@ MHB_EXPORT int mhb_attention_tc(const void* q, const void* cache, void* out, con
     a.block_table = block_table; a.tok_part_row = tok_part_row; a.part_acc = part_acc; a.part_ml = part_ml;
     a.status = status; a.num_items = num_items; a.width = width; a.nq = nq;
     a.nkv = nkv; a.P = P; a.num_pages = num_pages; a.window = window; a.scale = scale;
-    return d == 128 ? launch<128>(map, a, num_items, stream) : launch<64>(map, a, num_items, stream);
+    a.sink = nullptr; a.gate = nullptr; a.gate_nsplit = 1; a.gate_ld = 0; a.gate_split_stride = 0;
+    return d == 128 ? launch<128, false>(map, a, num_items, stream) : launch<64, false>(map, a, num_items, stream);
+}
+
+// The same with the options (see EXT at the kernel): a sink per query head, a gate on the output, softmax
+// weights that keep 16 bits in the value product.  Keys and values are both d wide here.
+MHB_EXPORT int mhb_attention_tc_ext(const void* q, const void* cache, void* out, const int* items, int num_items,
+                                    const int* positions, const int* block_table, int width,
+                                    const int* tok_part_row, float* part_acc, float* part_ml, int nq, int nkv, int d,
+                                    int P, int num_pages, int window, float scale, const float* sink,
+                                    const float* gate, int gate_nsplit, long long gate_split_stride, int gate_ld,
+                                    int* status, cudaStream_t stream) {
+    if (num_items <= 0) return 0;
+    if (nkv <= 0 || nq % nkv) return fail("attention: %d query heads over %d KV heads", nq, nkv);
+    if (!mhb_attention_tc_supports(d, P))
+        return fail("attention_tc: head_dim %d with pages of %d keys is not built (head_dim 64 or 128, page size dividing 64)", d, P);
+    if (sink && !(scale > 0.f)) return fail("attention_tc: a sink needs a positive scale");
+    const long long total_rows = (long long)num_pages * 2 * nkv * P;
+    if (total_rows > 0x7fffffffLL) return fail("attention_tc: the pool has too many rows for one tensor map");
+    CUtensorMap map;
+    int rc = make_bf16_map(&map, cache, total_rows, d, d, P);
+    if (rc) return rc;
+    AttnArgs a;
+    a.q = (const __nv_bfloat16*)q; a.out = (__nv_bfloat16*)out; a.items = items; a.positions = positions;
+    a.block_table = block_table; a.tok_part_row = tok_part_row; a.part_acc = part_acc; a.part_ml = part_ml;
+    a.status = status; a.num_items = num_items; a.width = width; a.nq = nq;
+    a.nkv = nkv; a.P = P; a.num_pages = num_pages; a.window = window; a.scale = scale;
+    a.sink = sink; a.gate = gate; a.gate_nsplit = gate_nsplit; a.gate_ld = gate_ld;
+    a.gate_split_stride = (size_t)gate_split_stride;
+    return d == 128 ? launch<128, true>(map, a, num_items, stream) : launch<64, true>(map, a, num_items, stream);
 }

@@ -24,6 +24,7 @@
 // the segment of token t and seg_slot[s] its state slot.  A segment whose first token sits at position
 // 0 starts from a zero state whatever the slot holds.
 #include "common.cuh"
+#include "mma_helpers.cuh"
 
 using namespace mhb;
 
@@ -159,16 +160,29 @@ lightning_chunk_prefix_kernel(const LightArgs a, const int* __restrict__ seg_chu
     const float lam = a.decay[h];
     float* slot = a.state + ((size_t)a.seg_slot[seg] * a.H + h) * dk * dv;
     const bool fresh = a.positions[t0] == 0;
-    for (int idx = threadIdx.x; idx < dk * dv; idx += blockDim.x) {
-        float S = fresh ? 0.f : slot[idx];
-        for (int c = c0; c < c0 + nc; ++c) {
-            float* u = U + ((size_t)c * a.H + h) * dk * dv + idx;
-            const float own = *u;
-            *u = S;
-            S = fmaf(powf(lam, (float)chunks[4 * c + 2]), S, own);
+    // one element of the state per thread (blockIdx.z tiles the elements): the walk over the chunks is a
+    // chain of dependent sums, but its loads do not depend on it and are asked for eight chunks ahead
+    const int idx = blockIdx.z * blockDim.x + threadIdx.x;
+    if (idx >= dk * dv) return;
+    const int n_full = chunks[4 * c0 + 2];
+    const float lam_full = powf(lam, (float)n_full);
+    const size_t stride = (size_t)a.H * dk * dv;
+    float* u = U + ((size_t)c0 * a.H + h) * dk * dv + idx;
+    float S = fresh ? 0.f : slot[idx];
+    for (int c = 0; c < nc; c += 8) {
+        float own[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) own[i] = c + i < nc ? u[(size_t)(c + i) * stride] : 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (c + i < nc) {
+                u[(size_t)(c + i) * stride] = S;
+                const int n = chunks[4 * (c0 + c + i) + 2];
+                S = fmaf(n == n_full ? lam_full : powf(lam, (float)n), S, own[i]);
+            }
         }
-        if (a.writable) slot[idx] = S;
     }
+    if (a.writable) slot[idx] = S;
 }
 
 // ---- chunked: (3) outputs -----------------------------------------------------------------------------
@@ -218,6 +232,253 @@ lightning_chunk_out_kernel(const LightArgs a, const int* __restrict__ chunks, co
         for (int j = 0; j <= i; ++j) o = fmaf(Ai[j], vs[j * dv + e], o);
         a.out[(size_t)(t0 + i) * a.H * dv + h * dv + e] = o;
     }
+}
+
+
+// ---- chunked, on the tensor cores (the bfloat16 runtime) ---------------------------------------------------
+// The same three steps with mma.sync m16n8k16 (bfloat16 operands, float32 accumulation) for steps (1)
+// and (3); step (2) is the kernel above.  q, k and v are rounded to bfloat16 after silu (they are
+// activations of projections).  What the recurrence adds up stays at float32's reach: a float32 number
+// that must be an operand (a key times its power of lambda, a state, a decayed score) goes in as the sum
+// of two bfloat16 numbers, the rounded value and what the rounding lost, with a product for each (16
+// bits of mantissa instead of 8); powers of lambda, the masks and all sums are float32.
+// Chunks are 64 tokens; DK and DV are the widths padded to 32, 64 or 128 (the tails are zero).
+constexpr int TC_C = 64;
+
+__device__ __forceinline__ float load_raw(const LightArgs& a, size_t idx) {
+    float v = a.proj[idx];
+    for (int s = 1; s < a.nsplit; ++s) v += a.proj[idx + (size_t)s * a.split_stride];
+    return v;
+}
+
+// N * W values of the chunk's rows [t0, t0 + n) and columns [col0, col0 + w) of the product (zero outside),
+// through silu, handed to `put(row, column, value)`: eight loads are asked for before the first is used (a
+// thread that waits for every load in turn spends the kernel waiting).
+template <int W, typename Put>
+__device__ __forceinline__ void load_tile_silu(const LightArgs& a, int t0, int n, int col0, int w, Put put) {
+    constexpr int TOTAL = TC_C * W;
+    for (int base = 0; base < TOTAL; base += 128 * 8) {
+        float raw[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int idx = base + u * 128 + (int)threadIdx.x;
+            const int j = idx / W, e = idx - j * W;
+            raw[u] = (idx < TOTAL && j < n && e < w) ? load_raw(a, (size_t)(t0 + j) * a.ld + col0 + e) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int idx = base + u * 128 + (int)threadIdx.x;
+            const int j = idx / W, e = idx - j * W;
+            if (idx < TOTAL) put(j, e, siluf(raw[u]));
+        }
+    }
+}
+
+__device__ __forceinline__ void split_bf16(float v, __nv_bfloat16& hi, __nv_bfloat16& lo) {
+    hi = __float2bfloat16_rn(v);
+    lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+}
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(128)
+lightning_chunk_state_tc_kernel(const LightArgs a, const int* __restrict__ chunks, float* __restrict__ U) {
+    constexpr int LDK = DK + 8, LDV = DV + 8;
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    __nv_bfloat16* kh = (__nv_bfloat16*)smem_raw;          // [C][LDK] keys times lambda^(n-1-j), rounded
+    __nv_bfloat16* kl = kh + TC_C * LDK;                    // what the rounding lost
+    __nv_bfloat16* vs = kl + TC_C * LDK;                    // [C][LDV]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int c = blockIdx.x, h = blockIdx.y;
+    const int t0 = chunks[4 * c + 1], n = chunks[4 * c + 2];
+    const int dk = a.dk, dv = a.dv;
+    const float lam = a.decay[h];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    __shared__ float pw_s[TC_C];                  // lambda^(n-1-j)
+    if (tid < TC_C) pw_s[tid] = tid < n ? powf(lam, (float)(n - 1 - tid)) : 0.f;
+    __syncthreads();
+    // the key as the other kernel sees it (rounded once), times its power of lambda
+    load_tile_silu<DK>(a, t0, n, a.k0 + h * dk, dk, [&](int j, int e, float v) {
+        split_bf16(__bfloat162float(__float2bfloat16_rn(v)) * pw_s[j], kh[j * LDK + e], kl[j * LDK + e]);
+    });
+    load_tile_silu<DV>(a, t0, n, a.v0 + h * dv, dv, [&](int j, int e, float v) { vs[j * LDV + e] = __float2bfloat16_rn(v); });
+    __syncthreads();
+    // U [DK][DV] = K'^T V: warp w owns the rows w * DK/4 ... of U, in tiles of 16
+    constexpr int MT = DK / 64;            // 16-row tiles per warp (DK = 32: two warps have none)
+    constexpr int MTILES = MT > 0 ? MT : 1;
+    const uint32_t kh_s = (uint32_t)__cvta_generic_to_shared(kh), kl_s = (uint32_t)__cvta_generic_to_shared(kl);
+    const uint32_t v_s = (uint32_t)__cvta_generic_to_shared(vs);
+    if (DK == 32 && warp >= 2) return;
+    float u[MTILES][DV / 8][4];
+#pragma unroll
+    for (int m = 0; m < MTILES; ++m)
+#pragma unroll
+        for (int i = 0; i < DV / 8; ++i) u[m][i][0] = u[m][i][1] = u[m][i][2] = u[m][i][3] = 0.f;
+    const int row0 = DK == 32 ? warp * 16 : warp * (DK / 4);
+#pragma unroll
+    for (int ks = 0; ks < TC_C / 16; ++ks) {
+        uint32_t ah[MTILES][4], al[MTILES][4];
+#pragma unroll
+        for (int m = 0; m < MTILES; ++m) {
+            const int r = ks * 16 + (lane & 7) + 8 * (lane >> 4), cc = row0 + m * 16 + 8 * ((lane >> 3) & 1);
+            ldmatrix_x4_trans(kh_s + (r * LDK + cc) * 2, ah[m][0], ah[m][1], ah[m][2], ah[m][3]);
+            ldmatrix_x4_trans(kl_s + (r * LDK + cc) * 2, al[m][0], al[m][1], al[m][2], al[m][3]);
+        }
+#pragma unroll
+        for (int i = 0; i < DV / 8; i += 2) {
+            uint32_t b0, b1, b2, b3;
+            const int r = ks * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), cc = i * 8 + 8 * (lane >> 4);
+            ldmatrix_x4_trans(v_s + (r * LDV + cc) * 2, b0, b1, b2, b3);
+#pragma unroll
+            for (int m = 0; m < MTILES; ++m) {
+                mma_bf16(u[m][i], ah[m], b0, b1);
+                mma_bf16(u[m][i + 1], ah[m], b2, b3);
+                mma_bf16(u[m][i], al[m], b0, b1);
+                mma_bf16(u[m][i + 1], al[m], b2, b3);
+            }
+        }
+    }
+    float* dst = U + ((size_t)c * a.H + h) * dk * dv;
+#pragma unroll
+    for (int m = 0; m < MTILES; ++m)
+#pragma unroll
+        for (int i = 0; i < DV / 8; ++i)
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+                const int r = row0 + m * 16 + (lane >> 2) + 8 * (x >> 1), e = i * 8 + (lane & 3) * 2 + (x & 1);
+                if (r < dk && e < dv) dst[r * dv + e] = u[m][i][x];
+            }
+}
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(128)
+lightning_chunk_out_tc_kernel(const LightArgs a, const int* __restrict__ chunks, const float* __restrict__ U) {
+    constexpr int LDK = DK + 8, LDV = DV + 8;
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    __nv_bfloat16* qs = (__nv_bfloat16*)smem_raw;          // [C][LDK]
+    __nv_bfloat16* ks = qs + TC_C * LDK;                    // [C][LDK]
+    __nv_bfloat16* vs = ks + TC_C * LDK;                    // [C][LDV]
+    __nv_bfloat16* sh = vs + TC_C * LDV;                    // [DK][LDV] the state before the chunk, rounded
+    __nv_bfloat16* sl = sh + DK * LDV;                      // what the rounding lost
+    float* pw = (float*)(sl + DK * LDV);                    // [C + 1] powers of lambda
+    pdl_launch_dependents();
+    pdl_wait();
+    const int c = blockIdx.x, h = blockIdx.y;
+    const int t0 = chunks[4 * c + 1], n = chunks[4 * c + 2];
+    const int dk = a.dk, dv = a.dv;
+    const float lam = a.decay[h];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    load_tile_silu<DK>(a, t0, n, a.q0 + h * dk, dk, [&](int j, int e, float v) { qs[j * LDK + e] = __float2bfloat16_rn(v); });
+    load_tile_silu<DK>(a, t0, n, a.k0 + h * dk, dk, [&](int j, int e, float v) { ks[j * LDK + e] = __float2bfloat16_rn(v); });
+    load_tile_silu<DV>(a, t0, n, a.v0 + h * dv, dv, [&](int j, int e, float v) { vs[j * LDV + e] = __float2bfloat16_rn(v); });
+    const float* S = U + ((size_t)c * a.H + h) * dk * dv;
+    for (int base = 0; base < DK * DV; base += 128 * 8) {
+        float raw[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int idx = base + u * 128 + tid;
+            const int r = idx / DV, e = idx - r * DV;
+            raw[u] = (idx < DK * DV && r < dk && e < dv) ? S[r * dv + e] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int idx = base + u * 128 + tid;
+            const int r = idx / DV, e = idx - r * DV;
+            if (idx < DK * DV) split_bf16(raw[u], sh[r * LDV + e], sl[r * LDV + e]);
+        }
+    }
+    for (int i = tid; i <= TC_C; i += 128) pw[i] = powf(lam, (float)i);
+    __syncthreads();
+    const uint32_t q_s = (uint32_t)__cvta_generic_to_shared(qs), k_s = (uint32_t)__cvta_generic_to_shared(ks);
+    const uint32_t v_s = (uint32_t)__cvta_generic_to_shared(vs);
+    const uint32_t sh_s = (uint32_t)__cvta_generic_to_shared(sh), sl_s = (uint32_t)__cvta_generic_to_shared(sl);
+    const int wrow = warp * 16;                 // this warp's 16 tokens of the chunk
+    if (wrow >= n) return;
+    constexpr int KSTEPS = DK / 16, DTILES = DV / 8;
+    uint32_t qf[KSTEPS][4];
+#pragma unroll
+    for (int k = 0; k < KSTEPS; ++k) {
+        const int r = wrow + (lane & 7) + 8 * ((lane >> 3) & 1), cc = k * 16 + 8 * (lane >> 4);
+        ldmatrix_x4(q_s + (r * LDK + cc) * 2, qf[k][0], qf[k][1], qf[k][2], qf[k][3]);
+    }
+    // what the state before the chunk gives: o = lambda^(i+1) (q_i^T S)
+    float o[DTILES][4];
+#pragma unroll
+    for (int i = 0; i < DTILES; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+#pragma unroll
+    for (int k = 0; k < KSTEPS; ++k) {
+#pragma unroll
+        for (int i = 0; i < DTILES; i += 2) {
+            uint32_t b0, b1, b2, b3;
+            const int r = k * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), cc = i * 8 + 8 * (lane >> 4);
+            ldmatrix_x4_trans(sh_s + (r * LDV + cc) * 2, b0, b1, b2, b3);
+            mma_bf16(o[i], qf[k], b0, b1);
+            mma_bf16(o[i + 1], qf[k], b2, b3);
+            ldmatrix_x4_trans(sl_s + (r * LDV + cc) * 2, b0, b1, b2, b3);
+            mma_bf16(o[i], qf[k], b0, b1);
+            mma_bf16(o[i + 1], qf[k], b2, b3);
+        }
+    }
+    const int ra = wrow + (lane >> 2), rb = ra + 8;          // this thread's two rows
+    {
+        const float fa = pw[ra + 1], fb = pw[rb + 1];
+#pragma unroll
+        for (int i = 0; i < DTILES; ++i) { o[i][0] *= fa; o[i][1] *= fa; o[i][2] *= fb; o[i][3] *= fb; }
+    }
+    // the chunk's own tokens: scores against the keys up to this warp's last row, decayed, times the values
+#pragma unroll
+    for (int kb = 0; kb < TC_C / 16; ++kb) {          // 16 keys at a time
+        if (kb * 16 > wrow + 15) break;                 // keys after the warp's rows: masked anyway
+        float s[2][4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+        for (int k = 0; k < KSTEPS; k += 2) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                uint32_t b0, b1, b2, b3;
+                const int r = kb * 16 + j * 8 + (lane & 7), cc = k * 16 + 8 * (lane >> 3);
+                ldmatrix_x4(k_s + (r * LDK + cc) * 2, b0, b1, b2, b3);
+                mma_bf16(s[j], qf[k], b0, b1);
+                mma_bf16(s[j], qf[k + 1], b2, b3);
+            }
+        }
+        uint32_t ph[4], pl[4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            float p[4];
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+                const int row = x < 2 ? ra : rb;
+                const int col = kb * 16 + j * 8 + (lane & 3) * 2 + (x & 1);
+                p[x] = col <= row ? s[j][x] * pw[row - col] : 0.f;
+            }
+            __nv_bfloat16 hi[4], lo[4];
+#pragma unroll
+            for (int x = 0; x < 4; ++x) split_bf16(p[x], hi[x], lo[x]);
+            ph[j * 2 + 0] = (uint32_t)__bfloat16_as_ushort(hi[0]) | ((uint32_t)__bfloat16_as_ushort(hi[1]) << 16);
+            ph[j * 2 + 1] = (uint32_t)__bfloat16_as_ushort(hi[2]) | ((uint32_t)__bfloat16_as_ushort(hi[3]) << 16);
+            pl[j * 2 + 0] = (uint32_t)__bfloat16_as_ushort(lo[0]) | ((uint32_t)__bfloat16_as_ushort(lo[1]) << 16);
+            pl[j * 2 + 1] = (uint32_t)__bfloat16_as_ushort(lo[2]) | ((uint32_t)__bfloat16_as_ushort(lo[3]) << 16);
+        }
+#pragma unroll
+        for (int i = 0; i < DTILES; i += 2) {
+            uint32_t b0, b1, b2, b3;
+            const int r = kb * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), cc = i * 8 + 8 * (lane >> 4);
+            ldmatrix_x4_trans(v_s + (r * LDV + cc) * 2, b0, b1, b2, b3);
+            mma_bf16(o[i], ph, b0, b1);
+            mma_bf16(o[i + 1], ph, b2, b3);
+            mma_bf16(o[i], pl, b0, b1);
+            mma_bf16(o[i + 1], pl, b2, b3);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < DTILES; ++i)
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+            const int row = x < 2 ? ra : rb, e = i * 8 + (lane & 3) * 2 + (x & 1);
+            if (row < n && e < dv) a.out[(size_t)(t0 + row) * a.H * dv + h * dv + e] = o[i][x];
+        }
 }
 
 template <typename Kern>
@@ -280,8 +541,56 @@ MHB_EXPORT int mhb_lightning_chunked(const float* proj, int nsplit, long long sp
     if (allow_smem(lightning_chunk_out_kernel, s3, "lightning_chunk_out")) return -1;
     launch_kernel(lightning_chunk_state_kernel, dim3(num_chunks, H), dim3(256), s1, stream, a, chunks, U, C);
     if (check_launch("lightning_chunk_state")) return -1;
-    launch_kernel(lightning_chunk_prefix_kernel, dim3(num_segs, H), dim3(256), 0, stream, a, seg_chunks, chunks, U);
+    launch_kernel(lightning_chunk_prefix_kernel, dim3(num_segs, H, (dk * dv + 255) / 256), dim3(256), 0, stream, a, seg_chunks, chunks, U);
     if (check_launch("lightning_chunk_prefix")) return -1;
     launch_kernel(lightning_chunk_out_kernel, dim3(num_chunks, H), dim3(256), s3, stream, a, chunks, (const float*)U, C);
     return check_launch("lightning_chunk_out");
+}
+
+namespace {
+template <int DK, int DV>
+int launch_chunked_tc(const LightArgs& a, const int* chunks, int num_chunks, const int* seg_chunks, int num_segs,
+                      float* U, cudaStream_t stream) {
+    constexpr size_t s1 = 2 * ((size_t)2 * TC_C * (DK + 8) + (size_t)TC_C * (DV + 8));
+    constexpr size_t s3 = 2 * ((size_t)2 * TC_C * (DK + 8) + (size_t)TC_C * (DV + 8) + (size_t)2 * DK * (DV + 8)) + 4 * (TC_C + 1);
+    if (allow_smem(lightning_chunk_state_tc_kernel<DK, DV>, s1, "lightning_chunk_state_tc")) return -1;
+    if (allow_smem(lightning_chunk_out_tc_kernel<DK, DV>, s3, "lightning_chunk_out_tc")) return -1;
+    launch_kernel(lightning_chunk_state_tc_kernel<DK, DV>, dim3(num_chunks, a.H), dim3(128), s1, stream, a, chunks, U);
+    if (check_launch("lightning_chunk_state_tc")) return -1;
+    launch_kernel(lightning_chunk_prefix_kernel, dim3(num_segs, a.H, (a.dk * a.dv + 255) / 256), dim3(256), 0, stream, a, seg_chunks, chunks, U);
+    if (check_launch("lightning_chunk_prefix")) return -1;
+    launch_kernel(lightning_chunk_out_tc_kernel<DK, DV>, dim3(num_chunks, a.H), dim3(128), s3, stream, a, chunks, (const float*)U);
+    return check_launch("lightning_chunk_out_tc");
+}
+template <int DK>
+int dispatch_tc_dv(int dvp, const LightArgs& a, const int* chunks, int num_chunks, const int* seg_chunks, int num_segs,
+                   float* U, cudaStream_t stream) {
+    switch (dvp) {
+        case 32: return launch_chunked_tc<DK, 32>(a, chunks, num_chunks, seg_chunks, num_segs, U, stream);
+        case 64: return launch_chunked_tc<DK, 64>(a, chunks, num_chunks, seg_chunks, num_segs, U, stream);
+        case 128: return launch_chunked_tc<DK, 128>(a, chunks, num_chunks, seg_chunks, num_segs, U, stream);
+    }
+    return fail("lightning_chunked_tc: values %d wide", dvp);
+}
+int pad_width(int d) { return d <= 32 ? 32 : d <= 64 ? 64 : 128; }
+}  // namespace
+
+MHB_EXPORT int mhb_lightning_chunked_tc_supports(int dk, int dv) { return dk >= 1 && dk <= 128 && dv >= 1 && dv <= 128; }
+
+// The chunked route on the tensor cores; chunks of exactly 64 tokens (the last of a segment may be shorter).
+MHB_EXPORT int mhb_lightning_chunked_tc(const float* proj, int nsplit, long long split_stride, int ld, int q0, int k0,
+                                        int v0, const float* decay, float* state, float* out, const int* tok_seg,
+                                        const int* seg_slot, const int* positions, int T, int H, int dk, int dv,
+                                        int writable, const int* chunks, int num_chunks, const int* seg_chunks,
+                                        int num_segs, float* U, cudaStream_t stream) {
+    if (num_chunks <= 0 || num_segs <= 0) return 0;
+    if (H > 65535) return fail("lightning: too many heads");
+    if (!mhb_lightning_chunked_tc_supports(dk, dv)) return fail("lightning_chunked_tc: widths %d and %d (up to 128)", dk, dv);
+    const LightArgs a = make_args(proj, nsplit, split_stride, ld, q0, k0, v0, decay, state, out, tok_seg, seg_slot,
+                                  positions, T, H, dk, dv, writable);
+    switch (pad_width(dk)) {
+        case 32: return dispatch_tc_dv<32>(pad_width(dv), a, chunks, num_chunks, seg_chunks, num_segs, U, stream);
+        case 64: return dispatch_tc_dv<64>(pad_width(dv), a, chunks, num_chunks, seg_chunks, num_segs, U, stream);
+        default: return dispatch_tc_dv<128>(pad_width(dv), a, chunks, num_chunks, seg_chunks, num_segs, U, stream);
+    }
 }

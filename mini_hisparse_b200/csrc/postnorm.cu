@@ -39,6 +39,32 @@ __device__ __forceinline__ float gelu_tanhf(float z) {
     return 0.5f * z * (1.f + tanhf(c * (z + 0.044715f * z * z * z)));
 }
 
+template <typename T> __device__ __forceinline__ float4 load4(const T* p);
+template <> __device__ __forceinline__ float4 load4<float>(const float* p) { return *(const float4*)p; }
+template <> __device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* p) {
+    const uint2 u = *(const uint2*)p;
+    const __nv_bfloat162 a = *(const __nv_bfloat162*)&u.x, b = *(const __nv_bfloat162*)&u.y;
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+template <typename T> __device__ __forceinline__ void store4(T* p, float4 v);
+template <> __device__ __forceinline__ void store4<float>(float* p, float4 v) { *(float4*)p = v; }
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *(const uint32_t*)&a;
+    u.y = *(const uint32_t*)&b;
+    *(uint2*)p = u;
+}
+template <typename T>
+__device__ __forceinline__ float4 load4_parts(const T* p, size_t idx, int nsplit, size_t split_stride) {
+    float4 v = load4<T>(p + idx);
+    for (int s = 1; s < nsplit; ++s) {
+        const float4 w = load4<T>(p + idx + (size_t)s * split_stride);
+        v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
+    }
+    return v;
+}
+
 // ---- x <- keep x + rms(alpha x + delta) w ---------------------------------------------------------
 template <typename DT, typename OT>
 __global__ void norm_mix_kernel(float* __restrict__ x, const DT* __restrict__ delta, int nsplit,
@@ -67,6 +93,45 @@ __global__ void norm_mix_kernel(float* __restrict__ x, const DT* __restrict__ de
     }
 }
 
+// The same with four elements per thread and step (H % 4 == 0, every row 16-byte aligned).
+template <typename DT, typename OT>
+__global__ void norm_mix_vec_kernel(float* __restrict__ x, const DT* __restrict__ delta, int nsplit,
+                                    size_t split_stride, const float* __restrict__ weight, float eps,
+                                    float alpha, float keep, OT* __restrict__ copy, int H) {
+    extern __shared__ float row[];
+    __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t r = blockIdx.x;
+    float* xr = x + r * H;
+    float ss = 0.f;
+    for (int i = 4 * threadIdx.x; i < H; i += 4 * blockDim.x) {
+        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (alpha != 0.f) {
+            const float4 v = *(const float4*)(xr + i);
+            s = make_float4(alpha * v.x, alpha * v.y, alpha * v.z, alpha * v.w);
+        }
+        if (delta) {
+            const float4 d = load4_parts(delta, r * H + i, nsplit, split_stride);
+            s.x += d.x; s.y += d.y; s.z += d.z; s.w += d.w;
+        }
+        *(float4*)(row + i) = s;
+        ss += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
+    }
+    const float total = block_sum(ss, scratch);
+    const float rstd = 1.f / sqrtf(total / (float)H + eps);
+    for (int i = 4 * threadIdx.x; i < H; i += 4 * blockDim.x) {
+        const float4 s = *(const float4*)(row + i), w = *(const float4*)(weight + i);
+        float4 n = make_float4(s.x * rstd * w.x, s.y * rstd * w.y, s.z * rstd * w.z, s.w * rstd * w.w);
+        if (keep != 0.f) {
+            const float4 v = *(const float4*)(xr + i);
+            n.x += keep * v.x; n.y += keep * v.y; n.z += keep * v.z; n.w += keep * v.w;
+        }
+        *(float4*)(xr + i) = n;
+        if (copy) store4<OT>(copy + r * H + i, n);
+    }
+}
+
 // ---- activations of a product ----------------------------------------------------------------------
 enum { ACT_RELU2 = 0, ACT_SILU = 1, ACT_GELU_TANH = 2, ACT_COPY = 3 };
 
@@ -84,6 +149,25 @@ __global__ void act_rows_kernel(const IT* __restrict__ z, int nsplit, size_t spl
     else if (act == ACT_GELU_TANH) a = gelu_tanhf(v);
     else a = v;
     out[i] = from_float<OT>(a);
+}
+
+__device__ __forceinline__ float act_of(float v, int act) {
+    if (act == ACT_RELU2) { const float a = fmaxf(v, 0.f); return a * a; }
+    if (act == ACT_SILU) return v * sigmoidf(v);
+    if (act == ACT_GELU_TANH) return gelu_tanhf(v);
+    return v;
+}
+
+// four elements per thread (n % 4 == 0, 16-byte aligned, parts a multiple of four elements apart)
+template <typename IT, typename OT>
+__global__ void act_rows_vec_kernel(const IT* __restrict__ z, int nsplit, size_t split_stride, OT* __restrict__ out,
+                                    size_t n, int act) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t i = 4 * ((size_t)blockIdx.x * blockDim.x + threadIdx.x);
+    if (i >= n) return;
+    const float4 v = load4_parts(z, i, nsplit, split_stride);
+    store4<OT>(out + i, make_float4(act_of(v.x, act), act_of(v.y, act), act_of(v.z, act), act_of(v.w, act)));
 }
 
 // ---- gelu_tanh(z) * table[token, column0 + j] -------------------------------------------------------
@@ -233,6 +317,20 @@ MHB_EXPORT int mhb_norm_mix(float* x, const void* delta, int delta_dtype, int ns
     if (R <= 0) return 0;
     if (nsplit > 1 && delta_dtype != MHB_F32) return fail("norm_mix: split partials must be float32");
     const size_t smem = sizeof(float) * (size_t)H;
+    const bool vec = H % 4 == 0 && !((uintptr_t)x & 15) && !((uintptr_t)delta & 15) && !((uintptr_t)weight & 15) &&
+                     !((uintptr_t)copy & 15) && split_stride % 4 == 0;
+    if (vec) {
+        int threads = (H / 4 + 31) / 32 * 32;
+        if (threads > 512) threads = 512;
+        if (threads < 64) threads = 64;
+        MHB_DISPATCH_DTYPE(delta_dtype, DT, MHB_DISPATCH_DTYPE(copy_dtype, OT, {
+            auto kern = norm_mix_vec_kernel<DT, OT>;
+            if (allow_smem(kern, smem, "norm_mix")) return -1;
+            launch_kernel(kern, dim3(R), dim3(threads), smem, stream, x, (const DT*)delta, nsplit,
+                          (size_t)split_stride, weight, eps, alpha, keep, (OT*)copy, H);
+        }));
+        return check_launch("norm_mix");
+    }
     MHB_DISPATCH_DTYPE(delta_dtype, DT, MHB_DISPATCH_DTYPE(copy_dtype, OT, {
         auto kern = norm_mix_kernel<DT, OT>;
         if (allow_smem(kern, smem, "norm_mix")) return -1;
@@ -248,6 +346,13 @@ MHB_EXPORT int mhb_act_rows(const void* z, int in_dtype, int nsplit, long long s
     if (act < 0 || act > ACT_COPY) return fail("act_rows: unknown activation %d", act);
     if (nsplit > 1 && in_dtype != MHB_F32) return fail("act_rows: split partials must be float32");
     const int threads = 256;
+    if (n % 4 == 0 && !((uintptr_t)z & 15) && !((uintptr_t)out & 15) && split_stride % 4 == 0) {
+        const unsigned vblocks = (unsigned)((n / 4 + threads - 1) / threads);
+        MHB_DISPATCH_DTYPE(in_dtype, IT, MHB_DISPATCH_DTYPE(out_dtype, OT,
+            launch_kernel((act_rows_vec_kernel<IT, OT>), dim3(vblocks), dim3(threads), 0, stream, (const IT*)z, nsplit,
+                          (size_t)split_stride, (OT*)out, (size_t)n, act)));
+        return check_launch("act_rows");
+    }
     const unsigned blocks = (unsigned)((n + threads - 1) / threads);
     MHB_DISPATCH_DTYPE(in_dtype, IT, MHB_DISPATCH_DTYPE(out_dtype, OT,
         launch_kernel((act_rows_kernel<IT, OT>), dim3(blocks), dim3(threads), 0, stream, (const IT*)z, nsplit,

@@ -477,6 +477,30 @@ def attention_mma(q, cache, out, part_acc, part_ml, items, num_items, rows, posi
         "attention_mma")
 
 
+def lightning_chunked_tc_supports(dk: int, dv: int) -> bool:
+    """Widths the tensor-core chunked route takes (tiles padded to 32, 64 or 128)."""
+    return 1 <= dk <= 128 and 1 <= dv <= 128
+
+
+LIGHTNING_TC_CHUNK = 64
+
+
+def lightning_chunked_tc(proj, q0, k0, v0, decay, state, out, tok_seg, seg_slot, positions, chunks, num_chunks,
+                         seg_chunks, num_segs, scratch, *, heads, dk, dv, nsplit=1, split_stride=0, writable=True):
+    """lightning_chunked on the tensor cores: chunks of LIGHTNING_TC_CHUNK tokens, q, k and v rounded to
+    bfloat16 after silu, every float32 operand of a product as the sum of two bfloat16 numbers."""
+    lib = build.load("lightning")
+    T = out.shape[0]
+    if scratch.dtype != torch.float32 or scratch.numel() < num_chunks * heads * dk * dv:
+        raise KernelError("lightning_chunked_tc: the scratch is too small")
+    head = _lightning_head(proj, q0, k0, v0, decay, state, out, (tok_seg, seg_slot, positions), heads, dk, dv,
+                           nsplit, split_stride, writable)
+    _check(lib, lib.mhb_lightning_chunked_tc(*head, c_int(T), c_int(heads), c_int(dk), c_int(dv),
+                                             c_int(1 if writable else 0), _ptr(chunks), c_int(num_chunks),
+                                             _ptr(seg_chunks), c_int(num_segs), _ptr(scratch), _stream()),
+           "lightning_chunked_tc")
+
+
 def attention_mma_ext_supports(d: int, dv: int) -> bool:
     """Widths of keys and values the tensor-core attention with options takes (tiles padded to multiples of 32)."""
     return 8 <= d <= 128 and d % 8 == 0 and 8 <= dv <= 128 and dv % 8 == 0
@@ -606,6 +630,24 @@ def attention_tc(q, cache, out, items, num_items, positions, block_table, *, nq,
         c_int(block_table.shape[-1]), _ptr(tok_part_row), _ptr(part_acc), _ptr(part_ml),
         c_int(nq), c_int(nkv), c_int(d), c_int(page_size),
         c_int(cache.shape[0]), c_int(window or 0), c_float(scale), _ptr(status), _stream()), "attention_tc")
+
+
+def attention_tc_ext(q, cache, out, items, num_items, positions, block_table, *, nq, nkv, d, page_size,
+                     window=0, scale=None, status=None, part_acc=None, part_ml=None, tok_part_row=None,
+                     sink=None, gate=None, gate_nsplit=1, gate_split_stride=0):
+    """attention_tc with a ``sink`` per query head, a ``gate`` on the output and softmax weights that keep 16
+    bits in the value product; keys and values are both ``d`` wide."""
+    lib = build.load("attention_tc")
+    if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or not cache.is_contiguous():
+        raise KernelError("attention_tc_ext: q and the (contiguous) pool must be bfloat16")
+    if scale is None:
+        scale = float(d) ** -0.5
+    g = _gate_args(gate, gate_nsplit, gate_split_stride)
+    _check(lib, lib.mhb_attention_tc_ext(
+        _ptr(q), _ptr(cache), _ptr(out), _ptr(items), c_int(num_items), _ptr(positions), _ptr(block_table),
+        c_int(block_table.shape[-1]), _ptr(tok_part_row), _ptr(part_acc), _ptr(part_ml),
+        c_int(nq), c_int(nkv), c_int(d), c_int(page_size), c_int(cache.shape[0]), c_int(window or 0),
+        c_float(scale), _ptr(sink), g[0], g[1], g[2], g[3], _ptr(status), _stream()), "attention_tc_ext")
 
 
 def attention_combine(part_acc, part_ml, tok_part_row, tok_nsplit, out, *, nq, d, every=0, gate=None,

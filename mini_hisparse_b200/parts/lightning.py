@@ -87,8 +87,17 @@ class LightningAttention(Mixer):
     def planner(self, page_size: int, sm_count: int):
         return ChunkPlanner(self._chunk())
 
+    @property
+    def tensor_cores(self) -> bool:
+        """The chunked route on the tensor cores: the bfloat16 runtime and widths up to 128."""
+        return (self.rt is not None and self.rt.dtype == torch.bfloat16
+                and K.lightning_chunked_tc_supports(self.dk, self.dv))
+
     def _chunk(self) -> int:
-        """Tokens per chunk of the chunked route: the largest of 64, 32, 16 whose tiles fit an SM."""
+        """Tokens per chunk of the chunked route: the tensor-core kernels' 64, or on the CUDA cores the
+        largest of 64, 32, 16 whose tiles fit an SM."""
+        if self.tensor_cores:
+            return K.LIGHTNING_TC_CHUNK
         if not self.chunk:
             self.chunk = 16
             for c in (64, 32):
@@ -124,8 +133,12 @@ class LightningAttention(Mixer):
             K.lightning_scan(*args, **common, max_tokens=SCAN_MAX_TOKENS if n_chunks else 0)
         if n_chunks:
             scratch = ws.get("la_chunk_states", (n_chunks * self.heads * self.dk * self.dv,), torch.float32)
-            K.lightning_chunked(*args, meta["chunks"], n_chunks, meta["seg_chunks"], meta["num_long"], scratch,
-                                self._chunk(), **common)
+            if self.tensor_cores:
+                K.lightning_chunked_tc(*args, meta["chunks"], n_chunks, meta["seg_chunks"], meta["num_long"], scratch,
+                                       **common)
+            else:
+                K.lightning_chunked(*args, meta["chunks"], n_chunks, meta["seg_chunks"], meta["num_long"], scratch,
+                                    self._chunk(), **common)
         gate = (p[0] if proj.nsplit > 1 else p)[:, 2 * self.qw + self.vw:]
         out = ws.get("la_normed", (T, self.vw), rt.dtype)
         K.gated_rmsnorm(o, self.norm, self.eps, out, gate=gate, gate_nsplit=proj.nsplit,

@@ -52,17 +52,24 @@ class SinkAttention(Mixer):
         self.qw, self.kw, self.vw, self.ow = self.nq * self.dk, self.nkv * self.dk, self.nkv * self.dv, self.nq * self.dv
         self.weight = self.o_weight = self.q_norm = self.k_norm = self.sink = None
 
-    def kernel_family(self) -> str:
-        """"mma": the tensor-core kernel with options (bfloat16, widths that are multiples of 8 up to 128);
-        "simt": the CUDA-core kernel (float32, and every other width)."""
-        if self.rt is not None and self.rt.dtype == torch.bfloat16 and K.attention_mma_ext_supports(self.dk, self.dv):
-            return "mma"
-        return "simt"
+    def kernel_family(self, page_size: int | None = None) -> str:
+        """Which attention kernels serve this layer over pages of ``page_size`` keys (None: whatever the
+        page size).  "tc": tcgen05 128-row tiles for long portions (bfloat16, keys and values both 64 or
+        both 128 wide, pages that divide 64) and mma.sync 16-row tiles for the rest; "mma": mma.sync tiles
+        of 64 and 16 rows (bfloat16, widths that are multiples of 8 up to 128); "simt": the CUDA cores
+        (float32, and every other width)."""
+        if self.rt is None or self.rt.dtype != torch.bfloat16 or not K.attention_mma_ext_supports(self.dk, self.dv):
+            return "simt"
+        if page_size is not None and self.dk == self.dv and K.attention_tma_supports(self.dk, page_size):
+            return "tc"
+        return "mma"
 
     def kernel_modules(self):
-        if self.kernel_family() == "mma":
-            return ("attention_simt", "attention_mma_ext", "postnorm")
-        return ("attention_simt", "postnorm")
+        if self.kernel_family() == "simt":
+            return ("attention_simt", "postnorm")
+        if self.dk == self.dv and self.dk in (64, 128):
+            return ("attention_simt", "attention_mma_ext", "attention_tc", "postnorm")
+        return ("attention_simt", "attention_mma_ext", "postnorm")
 
     def cache_need(self):
         return PagedKVNeed(kv_heads=self.nkv, head_dim=self.dk, window=self.keep, v_dim=self.dv)
@@ -71,7 +78,7 @@ class SinkAttention(Mixer):
         return ("sink_attention", self.nq, self.nkv, self.window)
 
     def planner(self, page_size: int, sm_count: int):
-        rows = 64 if self.kernel_family() == "mma" else ROW_TILE
+        rows = {"tc": 128, "mma": 64, "simt": ROW_TILE}[self.kernel_family(page_size)]
         return AttentionPlanner(AttentionShape(self.nq, self.nkv, self.window, rows), sm_count)
 
     def parameters(self):
@@ -113,7 +120,8 @@ class SinkAttention(Mixer):
         part_ml = ws.get("attn_part_ml", (part_rows, self.nq, 2), torch.float32)
         n_small, n_big = meta["n_small"], meta["n_big"]
         n = n_small + n_big
-        if self.kernel_family() == "mma":
+        family = self.kernel_family(cache.page_size)
+        if family != "simt":
             args = (q, cache.storage, attn, part_acc, part_ml)
             tail = (ctx.positions, meta["block_table"], meta["tok_part_row"])
             common = dict(nq=self.nq, nkv=self.nkv, d=self.dk, dv=self.dv, page_size=cache.page_size,
@@ -123,8 +131,17 @@ class SinkAttention(Mixer):
                 counters = ws.get_zeroed("attn_counters", (T * self.nkv * chunks,), torch.int32)
                 K.attention_mma_ext(*args, meta["items"], n_small, 16, *tail, **common,
                                     tok_nsplit=meta["tok_nsplit"], counters=counters)
-            if n_big:            # long portions: 64-row tiles
-                K.attention_mma_ext(*args, meta["items"][n_small * ITEM_INTS:], n_big, 64, *tail, **common)
+            big_items = meta["items"][n_small * ITEM_INTS:]
+            if n_big and family == "tc":       # long portions: tcgen05 128-row tiles, split along the keys when few
+                K.attention_tc_ext(q, cache.storage, attn, big_items, n_big, ctx.positions, meta["block_table"],
+                                   nq=self.nq, nkv=self.nkv, d=self.dk, page_size=cache.page_size,
+                                   window=self.window or 0, scale=self.scale, status=ctx.status, part_acc=part_acc,
+                                   part_ml=part_ml, tok_part_row=meta["tok_part_row"], sink=self.sink, **gate)
+                if meta.get("big_split"):
+                    K.attention_combine(part_acc, part_ml, meta["tok_part_row"], meta["tok_nsplit"], attn,
+                                        nq=self.nq, d=self.dv, **gate)
+            elif n_big:          # long portions: 64-row tiles
+                K.attention_mma_ext(*args, big_items, n_big, 64, *tail, **common)
             return rt.linear(attn, self.o_weight, ws, "mix_out")
         if n:
             K.attention_simt(q, cache.storage, attn, part_acc, part_ml, meta["items"], n, n, ctx.positions,

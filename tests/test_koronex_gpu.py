@@ -60,10 +60,16 @@ CFG_C = dict(architecture="Koronex", vocab=300, width=256, embedding=dict(scale=
              postln_alpha=3.0, token_side=dict(dim=32), layers=[
                  layer("lightning", light(2, 64, 128, [0.9, 0.99]), ff=512),
                  layer("attention", attn(8, 1, 64, 128, 70, 32, base=1e6, scale=0.125), ff=384)])
-CONFIGS = {"A": CFG_A, "B": CFG_B, "C": CFG_C}
+# D: keys and values of one width (64) over pages of 16: in bfloat16 long portions take the tcgen05 kernel.
+CFG_D = dict(architecture="Koronex", vocab=150, width=128, embedding=dict(scale=1.5), norm=dict(eps=1e-5),
+             postln_alpha=2.0, token_side=dict(dim=8), layers=[
+                 layer("attention", attn(4, 2, 64, 64, 90, 32, scale=0.2), ff=256),
+                 layer("lightning", light(2, 32, 64, [0.9, 0.98])),
+                 layer("attention", attn(4, 2, 64, 64, 40, 32, scale=0.2, kv_from=0), ff=128)])
+CONFIGS = {"A": CFG_A, "B": CFG_B, "C": CFG_C, "D": CFG_D}
 # A row's error: the root mean square of (got - plain) as a share of the row's root mean square.  float32:
 # every row within rounding of another summation order; this is the sharp comparison (a window one key off
-# moves a row by 50 times as much: see the sensitivity test).  bfloat16: rounding of the stream and of the
+# moves the logits by 25 times as much: see the sensitivity test).  bfloat16: rounding of the stream and of the
 # activations is amplified by peaked softmaxes and has a heavy tail over rows (a plain model that only
 # rounds the sublayers' inputs to bfloat16 shows a mean of 0.005 and worst rows of 0.03 to 0.1 on these
 # shapes, ten times the median at the same rows where the engine's worst are), so the mean over rows is
@@ -71,7 +77,7 @@ CONFIGS = {"A": CFG_A, "B": CFG_B, "C": CFG_C}
 # prompt in the same dtype (the same roundings, so only the order of sums differs), and the kernels' own
 # tests above.
 BF16_MEAN, BF16_WORST = 0.03, 0.6
-F32_ROW = 2e-5
+F32_ROW = 4e-5
 BF16_CUT = 0.1
 
 
@@ -230,6 +236,27 @@ def test_lightning_token_by_token_in_chunks_and_plain_agree(dk, dv, heads):
     for o, st in ((o1, st1), (o2, st2)):
         assert float((o.cpu().double() - refs).abs().max()) < 3e-6 * scale
         assert float((st.cpu().double() - ref_state).abs().max()) < 3e-6 * float(ref_state.abs().max())
+    # the chunked route on the tensor cores: q, k, v rounded to bfloat16 after silu (so is the plain copy here),
+    # everything else at 16 bits or better
+    zb = z.to(torch.bfloat16).double()
+    refs_b, ref_state_b = torch.zeros(T, heads * dv, dtype=torch.float64), state0.double().clone()
+    for sg in segs:
+        rows = slice(sg.offset, sg.offset + sg.count)
+        for h in range(heads):
+            src = z if sg.count <= 16 else zb                # the single token goes by the scan, unrounded
+            S0 = torch.zeros(dk, dv, dtype=torch.float64) if sg.start == 0 else state0[sg.slot, h].double()
+            o, Sn = plain_lightning(src[rows, h * dk:(h + 1) * dk], src[rows, heads * dk + h * dk: heads * dk + (h + 1) * dk],
+                                    src[rows, 2 * heads * dk + h * dv: 2 * heads * dk + (h + 1) * dv], float(decay[h]), S0)
+            refs_b[rows, h * dv:(h + 1) * dv] = o
+            ref_state_b[sg.slot, h] = Sn
+    st3, o3 = state0.cuda().clone(), torch.zeros(T, heads * dv, device="cuda")
+    arrays, facts = ChunkPlanner(K.LIGHTNING_TC_CHUNK).plan(segs, T)
+    K.lightning_scan(*args(st3, o3), **common, max_tokens=16)
+    scratch = torch.empty(facts["num_chunks"] * heads * dk * dv, device="cuda")
+    K.lightning_chunked_tc(*args(st3, o3), torch.from_numpy(arrays["chunks"]).cuda(), facts["num_chunks"],
+                           torch.from_numpy(arrays["seg_chunks"]).cuda(), facts["num_long"], scratch, **common)
+    assert float((o3.cpu().double() - refs_b).abs().max()) < 1e-4 * float(refs_b.abs().max())
+    assert float((st3.cpu().double() - ref_state_b).abs().max()) < 1e-4 * float(ref_state_b.abs().max())
 
 
 def plain_sink_attention(q, k, v, qpos, scale, window, sink):
@@ -249,9 +276,10 @@ def plain_sink_attention(q, k, v, qpos, scale, window, sink):
     return out
 
 
-@pytest.mark.parametrize("dtype,kernel", [(torch.float32, "simt"), (torch.bfloat16, "simt"), (torch.bfloat16, "mma")])
+@pytest.mark.parametrize("dtype,kernel", [(torch.float32, "simt"), (torch.bfloat16, "simt"), (torch.bfloat16, "mma"),
+                                          (torch.bfloat16, "tc")])
 @pytest.mark.parametrize("page_size,window,dk,dv", [(16, 48, 32, 48), (8, 33, 64, 128), (16, 300, 16, 16),
-                                                    (16, 70, 40, 24)])
+                                                    (16, 70, 40, 24), (16, 48, 64, 64), (32, 150, 128, 128)])
 def test_attention_kernels_at_the_windows_edges_with_a_sink(dtype, kernel, page_size, window, dk, dv):
     """Keys go through the norm-rotate-append kernel into shuffled pages; then a prompt portion and single
     decoded tokens attend.  The key just inside the window and the key just outside it are made to stand out
@@ -262,8 +290,11 @@ def test_attention_kernels_at_the_windows_edges_with_a_sink(dtype, kernel, page_
     from mini_hisparse_b200.parts.attention import AttentionShape, plan_attention
     from mini_hisparse_b200.parts.base import Segment
 
+    if kernel == "tc" and not (dk == dv and dk in (64, 128)):
+        pytest.skip("the tcgen05 kernel takes keys and values that are both 64 or both 128 wide")
     g = torch.Generator().manual_seed(4)
-    H, G, L, rdim, eps, scale = 4, 2, 200, 8, 1e-5, 0.4
+    H, G, L, rdim, eps = 4, 2, 200, 8, 1e-5
+    scale = 2.2 / math.sqrt(dk)                    # random scores have a deviation of 2.2: the made-up 8 and 10 stand out
     portion = 30                                   # the last `portion` positions are the step's own tokens
     pages = -(-L // page_size)
     table = torch.randperm(pages + 3, generator=g)[:pages].to(torch.int32)
@@ -316,7 +347,7 @@ def test_attention_kernels_at_the_windows_edges_with_a_sink(dtype, kernel, page_
                       plain_sink_attention(qc, kc, vc, torch.arange(L), scale, window - 1, sink.double()),
                       plain_sink_attention(qc, kc, vc, torch.arange(L), scale, window, sink.double() - 50)):
             assert float((wrong[probe] - right[probe]).abs().max()) > 0.2
-    shape = AttentionShape(H, G, window, 64 if kernel == "mma" else 16)
+    shape = AttentionShape(H, G, window, {"tc": 128, "mma": 64, "simt": 16}[kernel])
 
     def attend(segments, rows):
         T = sum(s.count for s in segments)
@@ -329,7 +360,7 @@ def test_attention_kernels_at_the_windows_edges_with_a_sink(dtype, kernel, page_
         positions = dev_i(torch.cat([torch.arange(s.start, s.start + s.count) for s in segments]))
         items = dev_i(torch.from_numpy(plan.items))
         common = dict(nq=H, nkv=G, d=dk, dv=dv, page_size=page_size, window=window, scale=scale, sink=sink.cuda())
-        if kernel == "mma":
+        if kernel in ("mma", "tc"):
             head = (q_all[rows].contiguous(), pool, o, part_acc, part_ml)
             tail = (positions, tables, dev_i(torch.from_numpy(plan.tok_part_row)))
             if plan.n_small:
@@ -337,7 +368,15 @@ def test_attention_kernels_at_the_windows_edges_with_a_sink(dtype, kernel, page_
                 K.attention_mma_ext(*head, items, plan.n_small, 16, *tail, **common,
                                     tok_nsplit=dev_i(torch.from_numpy(plan.tok_nsplit)), counters=counters)
                 assert int(counters.abs().sum()) == 0
-            if plan.n_big:
+            if plan.n_big and kernel == "tc":
+                status = torch.zeros(1, dtype=torch.int32, device="cuda")
+                K.attention_tc_ext(head[0], pool, o, items.view(-1)[plan.n_small * 8:], plan.n_big, positions, tables,
+                                   nq=H, nkv=G, d=dk, page_size=page_size, window=window, scale=scale, status=status,
+                                   part_acc=part_acc, part_ml=part_ml, tok_part_row=tail[2], sink=sink.cuda())
+                assert int(status) == 0
+                if plan.big_split:
+                    K.attention_combine(part_acc, part_ml, tail[2], dev_i(torch.from_numpy(plan.tok_nsplit)), o, nq=H, d=dv)
+            elif plan.n_big:
                 K.attention_mma_ext(*head, items.view(-1)[plan.n_small * 8:], plan.n_big, 64, *tail, **common)
             return o.float().cpu().double().view(T, H, dv)
         K.attention_simt(q_all[rows].contiguous(), pool, o, part_acc, part_ml, items, n, n,
@@ -370,7 +409,7 @@ def test_every_schedule_agrees_with_the_plain_model(models, name, dtype):
     folder, cfg, w = models[name]
     reqs = requests_for(cfg, [150, 1, 23, 97, 64, 2, 131])
     refs = {rid: P.forward(cfg, w, toks).float() for rid, toks in reqs.items()}
-    page = {"A": 16, "B": 8, "C": 32}[name]
+    page = {"A": 16, "B": 8, "C": 32, "D": 16}[name]
     whole = None
     for steps in (S.whole(reqs), S.tail_one_by_one(reqs, tail=45), S.changing_portions(reqs), S.mixed(reqs, seed=3)):
         got, runner, cache = run_steps(folder, dtype, steps, page_size=page)
@@ -399,13 +438,13 @@ def test_the_plain_model_is_sensitive_to_what_the_tests_are_for(models):
     for li, delta in ((0, 1), (0, -1), (2, 1), (2, -1)):
         c = copy.deepcopy(cfg)
         c["layers"][li]["mixer"]["mask"]["size"] += delta
-        assert moved(c) > 50 * F32_ROW
+        assert moved(c) > 25 * F32_ROW
     w2 = dict(w)
     w2["l0.mix.sink"] = w["l0.mix.sink"] - 30
-    assert moved(w2=w2) > 50 * F32_ROW
+    assert moved(w2=w2) > 25 * F32_ROW
     c = copy.deepcopy(cfg)
     c["layers"][1]["mixer"]["decay"] = [0.5, 0.9, 0.9]
-    assert moved(c) > 50 * F32_ROW
+    assert moved(c) > 25 * F32_ROW
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
