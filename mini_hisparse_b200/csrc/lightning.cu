@@ -254,20 +254,52 @@ __device__ __forceinline__ float load_raw(const LightArgs& a, size_t idx) {
 // N * W values of the chunk's rows [t0, t0 + n) and columns [col0, col0 + w) of the product (zero outside),
 // through silu, handed to `put(row, column, value)`: eight loads are asked for before the first is used (a
 // thread that waits for every load in turn spends the kernel waiting).
-template <int W, typename Put>
+template <int W, int NT, typename Put>
 __device__ __forceinline__ void load_tile_silu(const LightArgs& a, int t0, int n, int col0, int w, Put put) {
     constexpr int TOTAL = TC_C * W;
-    for (int base = 0; base < TOTAL; base += 128 * 8) {
+    // four elements a load where rows and columns allow it (16-byte aligned): a quarter of the requests
+    const bool vec = (w & 3) == 0 && (col0 & 3) == 0 && (a.ld & 3) == 0 && (a.split_stride & 3) == 0 &&
+                     ((uintptr_t)a.proj & 15) == 0;
+    if (vec) {
+        for (int base = 0; base < TOTAL; base += NT * 4 * 4) {
+            float4 raw[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int idx = base + (u * NT + (int)threadIdx.x) * 4;
+                const int j = idx / W, e = idx - j * W;
+                raw[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (idx < TOTAL && j < n && e < w) {
+                    const float* p = a.proj + (size_t)(t0 + j) * a.ld + col0 + e;
+                    raw[u] = *(const float4*)p;
+                    for (int s = 1; s < a.nsplit; ++s) {
+                        const float4 x = *(const float4*)(p + (size_t)s * a.split_stride);
+                        raw[u].x += x.x; raw[u].y += x.y; raw[u].z += x.z; raw[u].w += x.w;
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int idx = base + (u * NT + (int)threadIdx.x) * 4;
+                const int j = idx / W, e = idx - j * W;
+                if (idx < TOTAL) {
+                    put(j, e, siluf(raw[u].x)); put(j, e + 1, siluf(raw[u].y));
+                    put(j, e + 2, siluf(raw[u].z)); put(j, e + 3, siluf(raw[u].w));
+                }
+            }
+        }
+        return;
+    }
+    for (int base = 0; base < TOTAL; base += NT * 8) {
         float raw[8];
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-            const int idx = base + u * 128 + (int)threadIdx.x;
+            const int idx = base + u * NT + (int)threadIdx.x;
             const int j = idx / W, e = idx - j * W;
             raw[u] = (idx < TOTAL && j < n && e < w) ? load_raw(a, (size_t)(t0 + j) * a.ld + col0 + e) : 0.f;
         }
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-            const int idx = base + u * 128 + (int)threadIdx.x;
+            const int idx = base + u * NT + (int)threadIdx.x;
             const int j = idx / W, e = idx - j * W;
             if (idx < TOTAL) put(j, e, siluf(raw[u]));
         }
@@ -279,8 +311,11 @@ __device__ __forceinline__ void split_bf16(float v, __nv_bfloat16& hi, __nv_bflo
     lo = __float2bfloat16_rn(v - __bfloat162float(hi));
 }
 
+constexpr int STATE_THREADS = 128;      // four warps load, convert and multiply (eight were slower: 96 against 79 us)
+constexpr int OUT_THREADS = 512;        // all load and convert; the first eight warps multiply
+
 template <int DK, int DV>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(STATE_THREADS)
 lightning_chunk_state_tc_kernel(const LightArgs a, const int* __restrict__ chunks, float* __restrict__ U) {
     constexpr int LDK = DK + 8, LDV = DV + 8;
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -298,17 +333,17 @@ lightning_chunk_state_tc_kernel(const LightArgs a, const int* __restrict__ chunk
     if (tid < TC_C) pw_s[tid] = tid < n ? powf(lam, (float)(n - 1 - tid)) : 0.f;
     __syncthreads();
     // the key as the other kernel sees it (rounded once), times its power of lambda
-    load_tile_silu<DK>(a, t0, n, a.k0 + h * dk, dk, [&](int j, int e, float v) {
+    load_tile_silu<DK, STATE_THREADS>(a, t0, n, a.k0 + h * dk, dk, [&](int j, int e, float v) {
         split_bf16(__bfloat162float(__float2bfloat16_rn(v)) * pw_s[j], kh[j * LDK + e], kl[j * LDK + e]);
     });
-    load_tile_silu<DV>(a, t0, n, a.v0 + h * dv, dv, [&](int j, int e, float v) { vs[j * LDV + e] = __float2bfloat16_rn(v); });
+    load_tile_silu<DV, STATE_THREADS>(a, t0, n, a.v0 + h * dv, dv, [&](int j, int e, float v) { vs[j * LDV + e] = __float2bfloat16_rn(v); });
     __syncthreads();
     // U [DK][DV] = K'^T V: warp w owns the rows w * DK/4 ... of U, in tiles of 16
     constexpr int MT = DK / 64;            // 16-row tiles per warp (DK = 32: two warps have none)
     constexpr int MTILES = MT > 0 ? MT : 1;
     const uint32_t kh_s = (uint32_t)__cvta_generic_to_shared(kh), kl_s = (uint32_t)__cvta_generic_to_shared(kl);
     const uint32_t v_s = (uint32_t)__cvta_generic_to_shared(vs);
-    if (DK == 32 && warp >= 2) return;
+    if (warp >= 4 || (DK == 32 && warp >= 2)) return;
     float u[MTILES][DV / 8][4];
 #pragma unroll
     for (int m = 0; m < MTILES; ++m)
@@ -350,9 +385,13 @@ lightning_chunk_state_tc_kernel(const LightArgs a, const int* __restrict__ chunk
             }
 }
 
+// `staged`: the launch brought room for the chunk's raw float32 tiles: they are copied to shared memory by
+// cp.async, all requests in flight at once (one memory latency instead of one per batch of loads; with one
+// CTA of four warps per SM nothing else hides it), and converted from there.  Needs 16-byte aligned rows
+// and a product that is not split.
 template <int DK, int DV>
-__global__ void __launch_bounds__(128)
-lightning_chunk_out_tc_kernel(const LightArgs a, const int* __restrict__ chunks, const float* __restrict__ U) {
+__global__ void __launch_bounds__(OUT_THREADS)
+lightning_chunk_out_tc_kernel(const LightArgs a, const int* __restrict__ chunks, const float* __restrict__ U, int staged) {
     constexpr int LDK = DK + 8, LDV = DV + 8;
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __nv_bfloat16* qs = (__nv_bfloat16*)smem_raw;          // [C][LDK]
@@ -368,33 +407,99 @@ lightning_chunk_out_tc_kernel(const LightArgs a, const int* __restrict__ chunks,
     const int dk = a.dk, dv = a.dv;
     const float lam = a.decay[h];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    load_tile_silu<DK>(a, t0, n, a.q0 + h * dk, dk, [&](int j, int e, float v) { qs[j * LDK + e] = __float2bfloat16_rn(v); });
-    load_tile_silu<DK>(a, t0, n, a.k0 + h * dk, dk, [&](int j, int e, float v) { ks[j * LDK + e] = __float2bfloat16_rn(v); });
-    load_tile_silu<DV>(a, t0, n, a.v0 + h * dv, dv, [&](int j, int e, float v) { vs[j * LDV + e] = __float2bfloat16_rn(v); });
     const float* S = U + ((size_t)c * a.H + h) * dk * dv;
-    for (int base = 0; base < DK * DV; base += 128 * 8) {
-        float raw[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const int idx = base + u * 128 + tid;
-            const int r = idx / DV, e = idx - r * DV;
-            raw[u] = (idx < DK * DV && r < dk && e < dv) ? S[r * dv + e] : 0.f;
+    for (int i = tid; i <= TC_C; i += OUT_THREADS) pw[i] = powf(lam, (float)i);
+    if (staged) {
+        float* stage = pw + ((TC_C + 1 + 3) & ~3);                 // 16-byte aligned behind the powers
+        const uint32_t stage_s = (uint32_t)__cvta_generic_to_shared(stage);
+        auto issue = [&](int W, int col0, int w, int at) {
+            for (int idx = tid * 4; idx < TC_C * W; idx += OUT_THREADS * 4) {
+                const int j = idx / W, e = idx - j * W;
+                const bool live = j < n && e < w;
+                const float* src = live ? a.proj + (size_t)(t0 + j) * a.ld + col0 + e : a.proj;
+                cp_async16(stage_s + (at + idx) * 4, src, live ? 16 : 0);
+            }
+        };
+        issue(DK, a.q0 + h * dk, dk, 0);
+        issue(DK, a.k0 + h * dk, dk, TC_C * DK);
+        issue(DV, a.v0 + h * dv, dv, 2 * TC_C * DK);
+        cp_async_commit();
+        cp_async_wait<0>();
+        __syncthreads();
+        for (int idx = tid; idx < TC_C * DK; idx += OUT_THREADS) {
+            const int j = idx / DK, e = idx - j * DK;
+            qs[j * LDK + e] = __float2bfloat16_rn(siluf(stage[idx]));
+            ks[j * LDK + e] = __float2bfloat16_rn(siluf(stage[TC_C * DK + idx]));
         }
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const int idx = base + u * 128 + tid;
+        for (int idx = tid; idx < TC_C * DV; idx += OUT_THREADS) {
+            const int j = idx / DV, e = idx - j * DV;
+            vs[j * LDV + e] = __float2bfloat16_rn(siluf(stage[2 * TC_C * DK + idx]));
+        }
+        __syncthreads();                                            // the staging room is used again
+        for (int idx = tid * 4; idx < DK * DV; idx += OUT_THREADS * 4) {
             const int r = idx / DV, e = idx - r * DV;
-            if (idx < DK * DV) split_bf16(raw[u], sh[r * LDV + e], sl[r * LDV + e]);
+            const bool live = r < dk && e < dv;
+            cp_async16(stage_s + idx * 4, live ? S + r * dv + e : S, live ? 16 : 0);
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        __syncthreads();
+        for (int idx = tid; idx < DK * DV; idx += OUT_THREADS) {
+            const int r = idx / DV, e = idx - r * DV;
+            split_bf16(stage[idx], sh[r * LDV + e], sl[r * LDV + e]);
+        }
+    } else {
+    load_tile_silu<DK, OUT_THREADS>(a, t0, n, a.q0 + h * dk, dk, [&](int j, int e, float v) { qs[j * LDK + e] = __float2bfloat16_rn(v); });
+    load_tile_silu<DK, OUT_THREADS>(a, t0, n, a.k0 + h * dk, dk, [&](int j, int e, float v) { ks[j * LDK + e] = __float2bfloat16_rn(v); });
+    load_tile_silu<DV, OUT_THREADS>(a, t0, n, a.v0 + h * dv, dv, [&](int j, int e, float v) { vs[j * LDV + e] = __float2bfloat16_rn(v); });
+    if ((dv & 3) == 0 && (((uintptr_t)S) & 15) == 0) {
+        for (int base = 0; base < DK * DV; base += OUT_THREADS * 4 * 4) {
+            float4 raw[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int idx = base + (u * OUT_THREADS + tid) * 4;
+                const int r = idx / DV, e = idx - r * DV;
+                raw[u] = (idx < DK * DV && r < dk && e < dv) ? *(const float4*)(S + r * dv + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int idx = base + (u * OUT_THREADS + tid) * 4;
+                const int r = idx / DV, e = idx - r * DV;
+                if (idx < DK * DV) {
+                    split_bf16(raw[u].x, sh[r * LDV + e], sl[r * LDV + e]);
+                    split_bf16(raw[u].y, sh[r * LDV + e + 1], sl[r * LDV + e + 1]);
+                    split_bf16(raw[u].z, sh[r * LDV + e + 2], sl[r * LDV + e + 2]);
+                    split_bf16(raw[u].w, sh[r * LDV + e + 3], sl[r * LDV + e + 3]);
+                }
+            }
+        }
+    } else {
+        for (int base = 0; base < DK * DV; base += OUT_THREADS * 8) {
+            float raw[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int idx = base + u * OUT_THREADS + tid;
+                const int r = idx / DV, e = idx - r * DV;
+                raw[u] = (idx < DK * DV && r < dk && e < dv) ? S[r * dv + e] : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int idx = base + u * OUT_THREADS + tid;
+                const int r = idx / DV, e = idx - r * DV;
+                if (idx < DK * DV) split_bf16(raw[u], sh[r * LDV + e], sl[r * LDV + e]);
+            }
         }
     }
-    for (int i = tid; i <= TC_C; i += 128) pw[i] = powf(lam, (float)i);
+    }
     __syncthreads();
     const uint32_t q_s = (uint32_t)__cvta_generic_to_shared(qs), k_s = (uint32_t)__cvta_generic_to_shared(ks);
     const uint32_t v_s = (uint32_t)__cvta_generic_to_shared(vs);
     const uint32_t sh_s = (uint32_t)__cvta_generic_to_shared(sh), sl_s = (uint32_t)__cvta_generic_to_shared(sl);
-    const int wrow = warp * 16;                 // this warp's 16 tokens of the chunk
+    if (warp >= 8) return;
+    const int wrow = (warp & 3) * 16;           // this warp's 16 tokens of the chunk ...
     if (wrow >= n) return;
-    constexpr int KSTEPS = DK / 16, DTILES = DV / 8;
+    constexpr int KSTEPS = DK / 16, DTILES = DV / 16;     // ... and its half of the value columns
+    const int col0 = (warp >> 2) * (DV / 2);
     uint32_t qf[KSTEPS][4];
 #pragma unroll
     for (int k = 0; k < KSTEPS; ++k) {
@@ -410,7 +515,7 @@ lightning_chunk_out_tc_kernel(const LightArgs a, const int* __restrict__ chunks,
 #pragma unroll
         for (int i = 0; i < DTILES; i += 2) {
             uint32_t b0, b1, b2, b3;
-            const int r = k * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), cc = i * 8 + 8 * (lane >> 4);
+            const int r = k * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), cc = col0 + i * 8 + 8 * (lane >> 4);
             ldmatrix_x4_trans(sh_s + (r * LDV + cc) * 2, b0, b1, b2, b3);
             mma_bf16(o[i], qf[k], b0, b1);
             mma_bf16(o[i + 1], qf[k], b2, b3);
@@ -464,7 +569,7 @@ lightning_chunk_out_tc_kernel(const LightArgs a, const int* __restrict__ chunks,
 #pragma unroll
         for (int i = 0; i < DTILES; i += 2) {
             uint32_t b0, b1, b2, b3;
-            const int r = kb * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), cc = i * 8 + 8 * (lane >> 4);
+            const int r = kb * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), cc = col0 + i * 8 + 8 * (lane >> 4);
             ldmatrix_x4_trans(v_s + (r * LDV + cc) * 2, b0, b1, b2, b3);
             mma_bf16(o[i], ph, b0, b1);
             mma_bf16(o[i + 1], ph, b2, b3);
@@ -476,7 +581,7 @@ lightning_chunk_out_tc_kernel(const LightArgs a, const int* __restrict__ chunks,
     for (int i = 0; i < DTILES; ++i)
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
-            const int row = x < 2 ? ra : rb, e = i * 8 + (lane & 3) * 2 + (x & 1);
+            const int row = x < 2 ? ra : rb, e = col0 + i * 8 + (lane & 3) * 2 + (x & 1);
             if (row < n && e < dv) a.out[(size_t)(t0 + row) * a.H * dv + h * dv + e] = o[i][x];
         }
 }
@@ -554,12 +659,20 @@ int launch_chunked_tc(const LightArgs& a, const int* chunks, int num_chunks, con
     constexpr size_t s1 = 2 * ((size_t)2 * TC_C * (DK + 8) + (size_t)TC_C * (DV + 8));
     constexpr size_t s3 = 2 * ((size_t)2 * TC_C * (DK + 8) + (size_t)TC_C * (DV + 8) + (size_t)2 * DK * (DV + 8)) + 4 * (TC_C + 1);
     if (allow_smem(lightning_chunk_state_tc_kernel<DK, DV>, s1, "lightning_chunk_state_tc")) return -1;
-    if (allow_smem(lightning_chunk_out_tc_kernel<DK, DV>, s3, "lightning_chunk_out_tc")) return -1;
-    launch_kernel(lightning_chunk_state_tc_kernel<DK, DV>, dim3(num_chunks, a.H), dim3(128), s1, stream, a, chunks, U);
+    // room for the raw tiles of the staged route, if an SM has it and rows are 16-byte aligned
+    constexpr size_t stage_floats = (size_t)TC_C * (2 * DK + DV) > (size_t)DK * DV ? (size_t)TC_C * (2 * DK + DV) : (size_t)DK * DV;
+    constexpr size_t s3_staged = s3 + 16 + 4 * stage_floats;
+    const bool staged = s3_staged <= 227 * 1024 && a.nsplit == 1 && (a.dk & 3) == 0 && (a.dv & 3) == 0 && (a.ld & 3) == 0 &&
+                        (a.q0 & 3) == 0 && (a.k0 & 3) == 0 && (a.v0 & 3) == 0 && ((uintptr_t)a.proj & 15) == 0 &&
+                        ((uintptr_t)U & 15) == 0;
+    const size_t s3_used = staged ? s3_staged : s3;
+    if (allow_smem(lightning_chunk_out_tc_kernel<DK, DV>, s3_used, "lightning_chunk_out_tc")) return -1;
+    launch_kernel(lightning_chunk_state_tc_kernel<DK, DV>, dim3(num_chunks, a.H), dim3(STATE_THREADS), s1, stream, a, chunks, U);
     if (check_launch("lightning_chunk_state_tc")) return -1;
     launch_kernel(lightning_chunk_prefix_kernel, dim3(num_segs, a.H, (a.dk * a.dv + 255) / 256), dim3(256), 0, stream, a, seg_chunks, chunks, U);
     if (check_launch("lightning_chunk_prefix")) return -1;
-    launch_kernel(lightning_chunk_out_tc_kernel<DK, DV>, dim3(num_chunks, a.H), dim3(128), s3, stream, a, chunks, (const float*)U);
+    launch_kernel(lightning_chunk_out_tc_kernel<DK, DV>, dim3(num_chunks, a.H), dim3(OUT_THREADS), s3_used, stream, a, chunks,
+                  (const float*)U, staged ? 1 : 0);
     return check_launch("lightning_chunk_out_tc");
 }
 template <int DK>
