@@ -44,7 +44,21 @@ struct AttnArgs {
     int fresh;      // keys at positions > positions[tok0] - fresh may have been written by the kernel
                     // before this one (the append of this step); 0: any key may
     float scale;
+    // the options of a mixer that brings them (EXT instances only): a sink per query head in the softmax's
+    // denominator and a gate (columns of a float32 product, split-K parts summed in order) on the output
+    const float* sink;
+    const float* gate;
+    int gate_nsplit, gate_ld;
+    size_t gate_split_stride;
 };
+
+__device__ __forceinline__ float gate_of(const AttnArgs& a, int t, int col) {
+    if (!a.gate) return 1.f;
+    const size_t idx = (size_t)t * a.gate_ld + col;
+    float g = a.gate[idx];
+    for (int s = 1; s < a.gate_nsplit; ++s) g += a.gate[idx + (size_t)s * a.gate_split_stride];
+    return 1.f / (1.f + expf(-g));
+}
 
 template <int D, int ROWS>
 struct Layout {
@@ -66,7 +80,10 @@ __device__ __forceinline__ uint32_t swz(uint32_t base, int rows_per_half, int r,
 }
 __device__ __forceinline__ void compute_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CWARPS * 32) : "memory"); }
 
-template <int D, int ROWS>
+// EXT: the options.  The sink starts ONE thread's running (max, sum) of a row at (sink / scale, 1), in the
+// unsplit item or in split 0 only; the softmax's weights enter the value product as two bfloat16 numbers (the
+// weight and what rounding it lost: 16 bits instead of 8); the output is multiplied by sigmoid(gate).
+template <int D, int ROWS, bool EXT>
 __global__ void __launch_bounds__(THREADS, 2)
 attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a) {
     using L = Layout<D, ROWS>;
@@ -179,6 +196,18 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs 
 #pragma unroll
     for (int i = 0; i < DTILES; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    if constexpr (EXT) {
+        if (a.sink && split <= 0 && (!SPLIT_KEYS || warp == 0)) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int row = wrow + (lane >> 2) + 8 * h;
+                if (row < nrows) {
+                    m_run[h] = a.sink[kvh * groups + head0 + row % nheads] / a.scale;
+                    l_run[h] = (lane & 3) == 0 ? 1.f : 0.f;
+                }
+            }
+        }
+    }
     uint32_t qf[KSTEPS][4];
 #pragma unroll
     for (int k = 0; k < KSTEPS; ++k) {
@@ -236,6 +265,7 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs 
             l_run[h] *= alpha[h];
         }
         uint32_t pf[NT / 2][4];
+        uint32_t pl[EXT ? NT / 2 : 1][4];
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
             float p[4];
@@ -246,6 +276,13 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs 
             }
             pf[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p[0], p[1]);
             pf[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p[2], p[3]);
+            if constexpr (EXT) {
+                float r[4];
+#pragma unroll
+                for (int x = 0; x < 4; ++x) r[x] = p[x] - __bfloat162float(__float2bfloat16_rn(p[x]));
+                pl[j >> 1][(j & 1) * 2 + 0] = pack_bf16(r[0], r[1]);
+                pl[j >> 1][(j & 1) * 2 + 1] = pack_bf16(r[2], r[3]);
+            }
         }
 #pragma unroll
         for (int i = 0; i < DTILES; ++i) {
@@ -261,6 +298,10 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs 
                 ldmatrix_x4_trans(swz(v_s, KT, r, c), b0, b1, b2, b3);
                 mma_bf16(o[i], pf[kk], b0, b1);
                 mma_bf16(o[i + 1], pf[kk], b2, b3);
+                if constexpr (EXT) {
+                    mma_bf16(o[i], pl[kk], b0, b1);
+                    mma_bf16(o[i + 1], pl[kk], b2, b3);
+                }
             }
         }
         __syncwarp();
@@ -311,7 +352,9 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs 
             }
             const int t = tok0 + row / nheads, hq = kvh * groups + head0 + row % nheads;
             if (split < 0) {
-                a.out[((size_t)t * a.nq + hq) * D + e] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
+                float res = lsum > 0.f ? acc / lsum : 0.f;
+                if constexpr (EXT) res *= gate_of(a, t, hq * D + e);
+                a.out[((size_t)t * a.nq + hq) * D + e] = __float2bfloat16_rn(res);
             } else {
                 const size_t prow = (size_t)a.tok_part_row[t] + split;
                 a.part_acc[(prow * a.nq + hq) * D + e] = acc;
@@ -385,6 +428,10 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs 
                         }
                     }
                     const float inv = inv_s[row];
+                    if constexpr (EXT) {
+                        acc.x *= gate_of(a, t, hq * D + e); acc.y *= gate_of(a, t, hq * D + e + 1);
+                        acc.z *= gate_of(a, t, hq * D + e + 2); acc.w *= gate_of(a, t, hq * D + e + 3);
+                    }
                     uint2 packed;
                     packed.x = pack_bf16(acc.x * inv, acc.y * inv);
                     packed.y = pack_bf16(acc.z * inv, acc.w * inv);
@@ -422,9 +469,9 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs 
     }
 }
 
-template <int D, int ROWS>
+template <int D, int ROWS, bool EXT>
 int launch(const CUtensorMap& map, const AttnArgs& a, int launch_items, cudaStream_t stream) {
-    auto kern = attention_tma_kernel<D, ROWS>;
+    auto kern = attention_tma_kernel<D, ROWS, EXT>;
     constexpr int smem = Layout<D, ROWS>::TOTAL;
     static bool configured = false;
     if (!configured) {
@@ -469,6 +516,38 @@ MHB_EXPORT int mhb_attention_tma(const void* q, const void* cache, void* out, fl
     a.width = width; a.nq = nq; a.nkv = nkv; a.P = P; a.num_pages = num_pages; a.window = window;
     a.scale = scale;
     a.fresh = fresh;
-    if (rows == 16) return d == 128 ? launch<128, 16>(map, a, launch_items, stream) : launch<64, 16>(map, a, launch_items, stream);
+    a.sink = nullptr; a.gate = nullptr; a.gate_nsplit = 1; a.gate_ld = 0; a.gate_split_stride = 0;
+    if (rows == 16) return d == 128 ? launch<128, 16, false>(map, a, launch_items, stream) : launch<64, 16, false>(map, a, launch_items, stream);
+    return fail("attention_tma: tile height %d", rows);
+}
+
+// The same with the options (see EXT at the kernel); keys and values are both d wide.
+MHB_EXPORT int mhb_attention_tma_ext(const void* q, const void* cache, void* out, float* part_acc, float* part_ml,
+                                     const int* items, int num_items, int launch_items, int rows,
+                                     const int* positions, const int* block_table, int width,
+                                     const int* tok_part_row, const int* tok_nsplit, int* counters, int nq, int nkv,
+                                     int d, int P, int num_pages, int window, int fresh, float scale,
+                                     const float* sink, const float* gate, int gate_nsplit,
+                                     long long gate_split_stride, int gate_ld, int* status, cudaStream_t stream) {
+    if (launch_items <= 0) return 0;
+    if (nkv <= 0 || nq % nkv) return fail("attention: %d query heads over %d KV heads", nq, nkv);
+    if (!mhb_attention_tma_supports(d, P))
+        return fail("attention_tma: head_dim %d with pages of %d keys is not built (head_dim 64 or 128, page size dividing 64)", d, P);
+    if (sink && !(scale > 0.f)) return fail("attention_tma: a sink needs a positive scale");
+    const long long total_rows = (long long)num_pages * 2 * nkv * P;
+    if (total_rows > 0x7fffffffLL) return fail("attention_tma: the pool has too many rows for one tensor map");
+    CUtensorMap map;
+    int rc = make_bf16_map(&map, cache, total_rows, d, d, P);
+    if (rc) return rc;
+    AttnArgs a;
+    a.q = (const __nv_bfloat16*)q; a.out = (__nv_bfloat16*)out; a.part_acc = part_acc; a.part_ml = part_ml;
+    a.items = items; a.positions = positions; a.block_table = block_table; a.tok_part_row = tok_part_row;
+    a.tok_nsplit = tok_nsplit; a.counters = counters; a.status = status; a.num_items = num_items;
+    a.width = width; a.nq = nq; a.nkv = nkv; a.P = P; a.num_pages = num_pages; a.window = window;
+    a.scale = scale;
+    a.fresh = fresh;
+    a.sink = sink; a.gate = gate; a.gate_nsplit = gate_nsplit; a.gate_ld = gate_ld;
+    a.gate_split_stride = (size_t)gate_split_stride;
+    if (rows == 16) return d == 128 ? launch<128, 16, true>(map, a, launch_items, stream) : launch<64, 16, true>(map, a, launch_items, stream);
     return fail("attention_tma: tile height %d", rows);
 }

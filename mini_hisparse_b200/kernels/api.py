@@ -632,6 +632,25 @@ def attention_tc(q, cache, out, items, num_items, positions, block_table, *, nq,
         c_int(cache.shape[0]), c_int(window or 0), c_float(scale), _ptr(status), _stream()), "attention_tc")
 
 
+def attention_tma_ext(q, cache, out, part_acc, part_ml, items, num_items, rows, positions, block_table,
+                      tok_part_row, *, nq, nkv, d, page_size, window=0, scale=None, tok_nsplit=None,
+                      counters=None, status=None, fresh=0, sink=None, gate=None, gate_nsplit=1, gate_split_stride=0):
+    """attention_tma with a ``sink`` per query head, a ``gate`` on the output and softmax weights that keep 16
+    bits in the value product; keys and values are both ``d`` wide."""
+    lib = build.load("attention_tma")
+    if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or not cache.is_contiguous():
+        raise KernelError("attention_tma_ext: q and the (contiguous) pool must be bfloat16")
+    if scale is None:
+        scale = float(d) ** -0.5
+    g = _gate_args(gate, gate_nsplit, gate_split_stride)
+    _check(lib, lib.mhb_attention_tma_ext(
+        _ptr(q), _ptr(cache), _ptr(out), _ptr(part_acc), _ptr(part_ml), _ptr(items), c_int(num_items),
+        c_int(num_items), c_int(rows), _ptr(positions), _ptr(block_table), c_int(block_table.shape[-1]),
+        _ptr(tok_part_row), _ptr(tok_nsplit), _ptr(counters), c_int(nq), c_int(nkv), c_int(d),
+        c_int(page_size), c_int(cache.shape[0]), c_int(window or 0), c_int(fresh), c_float(scale), _ptr(sink),
+        g[0], g[1], g[2], g[3], _ptr(status), _stream()), "attention_tma_ext")
+
+
 def attention_tc_ext(q, cache, out, items, num_items, positions, block_table, *, nq, nkv, d, page_size,
                      window=0, scale=None, status=None, part_acc=None, part_ml=None, tok_part_row=None,
                      sink=None, gate=None, gate_nsplit=1, gate_split_stride=0):

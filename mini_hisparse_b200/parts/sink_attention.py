@@ -68,7 +68,7 @@ class SinkAttention(Mixer):
         if self.kernel_family() == "simt":
             return ("attention_simt", "postnorm")
         if self.dk == self.dv and self.dk in (64, 128):
-            return ("attention_simt", "attention_mma_ext", "attention_tc", "postnorm")
+            return ("attention_simt", "attention_mma_ext", "attention_tma", "attention_tc", "postnorm")
         return ("attention_simt", "attention_mma_ext", "postnorm")
 
     def cache_need(self):
@@ -129,8 +129,14 @@ class SinkAttention(Mixer):
             if n_small:          # decoded tokens and short portions: 16-row tiles, key splits merged by the last CTA
                 chunks = -(-(self.nq // self.nkv) // ROW_TILE)
                 counters = ws.get_zeroed("attn_counters", (T * self.nkv * chunks,), torch.int32)
-                K.attention_mma_ext(*args, meta["items"], n_small, 16, *tail, **common,
-                                    tok_nsplit=meta["tok_nsplit"], counters=counters)
+                if family == "tc":      # TMA-fed tiles (keys and values of one width, pages that divide 64)
+                    K.attention_tma_ext(*args, meta["items"], n_small, 16, *tail, nq=self.nq, nkv=self.nkv, d=self.dk,
+                                        page_size=cache.page_size, window=self.window or 0, scale=self.scale,
+                                        sink=self.sink, **gate, tok_nsplit=meta["tok_nsplit"], counters=counters,
+                                        status=ctx.status)
+                else:
+                    K.attention_mma_ext(*args, meta["items"], n_small, 16, *tail, **common,
+                                        tok_nsplit=meta["tok_nsplit"], counters=counters)
             big_items = meta["items"][n_small * ITEM_INTS:]
             if n_big and family == "tc":       # long portions: tcgen05 128-row tiles, split along the keys when few
                 K.attention_tc_ext(q, cache.storage, attn, big_items, n_big, ctx.positions, meta["block_table"],

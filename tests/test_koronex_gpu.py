@@ -365,8 +365,15 @@ def test_attention_kernels_at_the_windows_edges_with_a_sink(dtype, kernel, page_
             tail = (positions, tables, dev_i(torch.from_numpy(plan.tok_part_row)))
             if plan.n_small:
                 counters = torch.zeros(T * G, dtype=torch.int32, device="cuda")
-                K.attention_mma_ext(*head, items, plan.n_small, 16, *tail, **common,
-                                    tok_nsplit=dev_i(torch.from_numpy(plan.tok_nsplit)), counters=counters)
+                if kernel == "tc":
+                    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+                    K.attention_tma_ext(*head, items, plan.n_small, 16, *tail, nq=H, nkv=G, d=dk, page_size=page_size,
+                                        window=window, scale=scale, sink=sink.cuda(), status=status,
+                                        tok_nsplit=dev_i(torch.from_numpy(plan.tok_nsplit)), counters=counters)
+                    assert int(status) == 0
+                else:
+                    K.attention_mma_ext(*head, items, plan.n_small, 16, *tail, **common,
+                                        tok_nsplit=dev_i(torch.from_numpy(plan.tok_nsplit)), counters=counters)
                 assert int(counters.abs().sum()) == 0
             if plan.n_big and kernel == "tc":
                 status = torch.zeros(1, dtype=torch.int32, device="cuda")
