@@ -60,6 +60,8 @@ class SinkAttention(Mixer):
         (float32, and every other width)."""
         if self.rt is None or self.rt.dtype != torch.bfloat16 or not K.attention_mma_ext_supports(self.dk, self.dv):
             return "simt"
+        if not self.scale > 0.0:        # the tensor-core kernels keep the sink in the raw products' units, sink / scale
+            return "simt"
         if page_size is not None and self.dk == self.dv and K.attention_tma_supports(self.dk, page_size):
             return "tc"
         return "mma"
