@@ -72,7 +72,7 @@ class ActivatedMLP(FeedForward):
         z = rt.linear(h, self.up, ws, "ff_up", out_dtype=torch.float32)
         act = ws.get("ff_act", (h.shape[0], self.inter), rt.dtype)
         K.act_rows(z.tensor, act, self.activation, nsplit=z.nsplit, split_stride=z.split_stride)
-        return rt.linear(act, self.down, ws, "ff_out")
+        return rt.linear(act, self.down, ws, "ff_out", out_dtype=torch.float32)       # it joins a float32 sum
 
 
 @register_feed_forward("token_side")

@@ -143,4 +143,4 @@ class LightningAttention(Mixer):
         out = ws.get("la_normed", (T, self.vw), rt.dtype)
         K.gated_rmsnorm(o, self.norm, self.eps, out, gate=gate, gate_nsplit=proj.nsplit,
                         gate_split_stride=proj.split_stride)
-        return rt.linear(out, self.o_weight, ws, "mix_out")
+        return rt.linear(out, self.o_weight, ws, "mix_out", out_dtype=torch.float32)      # it joins a float32 sum

@@ -150,7 +150,7 @@ class SinkAttention(Mixer):
                                         nq=self.nq, d=self.dv, **gate)
             elif n_big:          # long portions: 64-row tiles
                 K.attention_mma_ext(*args, big_items, n_big, 64, *tail, **common)
-            return rt.linear(attn, self.o_weight, ws, "mix_out")
+            return rt.linear(attn, self.o_weight, ws, "mix_out", out_dtype=torch.float32)
         if n:
             K.attention_simt(q, cache.storage, attn, part_acc, part_ml, meta["items"], n, n, ctx.positions,
                              meta["block_table"], meta["tok_part_row"], nq=self.nq, nkv=self.nkv, d=self.dk,
@@ -159,4 +159,4 @@ class SinkAttention(Mixer):
         if meta["any_split"]:
             K.attention_combine(part_acc, part_ml, meta["tok_part_row"], meta["tok_nsplit"], attn, nq=self.nq,
                                 d=self.dv, **gate)
-        return rt.linear(attn, self.o_weight, ws, "mix_out")
+        return rt.linear(attn, self.o_weight, ws, "mix_out", out_dtype=torch.float32)
