@@ -174,7 +174,7 @@ attention_mma_kernel(const AttnArgs a) {
     const float scale_log2 = a.scale * 1.4426950408889634f;
     if constexpr (EXT) {
         // the sink is a score that is not scaled: in the units of the raw products it is sink / scale.  It
-        // counts once per row: in one warp (where four warps share the rows) and one thread of the quad.
+        // is added a single time per row: in one warp (where four warps share the rows) and one thread of the quad.
         if (a.sink && split <= 0 && (!SPLIT_KEYS || warp == 0)) {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {

@@ -18,8 +18,8 @@
 //   dv != d    values of another width than keys; a page then holds [keys: nkv][P][d] followed by
 //              [values: nkv][P][dv] (for dv == d that IS the layout [2][nkv][P][d])
 //   sink       one learned number per query head that joins the softmax's denominator as exp(sink_h)
-//              with no key and no value: the running (max, sum) starts at (sink_h, 1) instead of
-//              (-inf, 0), in the unsplit item or in split 0 only, so it counts once
+//              that stands for no position: the running (max, sum) starts at (sink_h, 1) instead of
+//              (-inf, 0), in the unsplit item or in split 0 only, so a token's parts hold it a single time
 //   gate       the output row is multiplied by sigmoid(gate[t][h * dv + e]); the gate comes as the
 //              columns of a float32 product (split-K parts summed in order)
 #include "common.cuh"
@@ -109,7 +109,7 @@ attention_simt_kernel(const AttnArgs a) {
 #pragma unroll
         for (int i = 0; i < DPL; ++i) acc[rs][i] = 0.f;
         const int r = rs * WARPS + warp;
-        if (a.sink && split <= 0 && r < nrows) {      // the sink counts once: here or in split 0
+        if (a.sink && split <= 0 && r < nrows) {      // a single time per token: here or in split 0
             m[rs] = a.sink[kvh * groups + head0 + r % nheads];
             l[rs] = 1.f;
         }

@@ -5,8 +5,8 @@
 //   S_t = lambda_h S_(t-1) + k_t v_t^T        S is [dk][dv], float32, one per request slot and head
 //   o_t = S_t^T q_t
 //
-// The state lives in float32 and everything that enters the recurrence is float32: the product's
-// float32 outputs (or split-K parts, summed in order) go through silu in float32; nothing is
+// S is kept as float32 and so is every term of its update and of o: the product's float32 outputs
+// (or split-K parts, summed in order) go through silu in float32; on the CUDA-core routes nothing is
 // rounded to a shorter type before it is added into S or o.
 //
 // Two routes give the same numbers up to float32 rounding:

@@ -100,7 +100,7 @@ def embed(table, tokens, out, status=None, scale: float = 1.0, copy=None):
 def norm_mix(x, weight, eps, *, delta=None, nsplit=1, split_stride=0, alpha=1.0, keep=0.0, copy=None):
     """x <- keep * x + rms(alpha * x + delta) * weight, row by row in float32, in place; ``copy`` (compute
     dtype, same shape) receives the new rows too.  alpha = 0 leaves x out of the norm (a normalised branch
-    that is ADDED to the stream: keep = 1); keep = 0 replaces the stream by the norm (norm after the sum).
+    that is ADDED to the stream: keep = 1); keep = 0 replaces the stream by the norm (a post-norm block).
     ``delta`` may be ``nsplit`` float32 partial matrices ``split_stride`` elements apart."""
     lib = build.load("postnorm")
     R, H = x.shape

@@ -1,7 +1,7 @@
 """Koronex as data: the ModelSpec of a KoronexConfig and its registry entry.
 
-The embedding is scaled; every layer is a post-norm block (norm after the sum, with a scale on the
-stream) whose mixer is lightning attention (linear attention with a decay per head, a state per
+The embedding is scaled; every layer is a post-norm block (the norm follows the residual addition, and the
+stream is scaled inside it) whose mixer is lightning attention (linear attention with a decay per head, a state per
 request) or windowed grouped-query attention with a norm over the whole q and k projections, partial
 rotation, a softmax sink and an output gate; a layer may have a relu-squared feed-forward, and ends
 with an input from the token itself (a slice of a table shared by all layers).  An attention layer

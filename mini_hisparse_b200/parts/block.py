@@ -39,12 +39,12 @@ class PreNormBlock(Block):
 
 @register_block("post_norm")
 class PostNormBlock(Block):
-    """Norm AFTER the sum, with a scale on the stream:
+    """Post-norm with a scaled stream (the norm comes behind the residual addition):
 
         x <- norm1(alpha x + mixer(x));   x <- norm2(alpha x + ff(x))  (if the layer has a feed-forward);
         x <- x + side(x)                  (if the layer has a "side" part: a normalised branch of its own)
 
-    The sublayers read the stream itself, so every kernel that writes the stream also leaves its rows
+    Mixer and feed-forward take the un-normalised stream as input, so every kernel that writes the stream also leaves its rows
     in the compute dtype (ctx.extras["x_copy"]; the float32 path reads the stream directly).  Roles:
     "mixer", "mixer_norm", and optionally "feed_forward" with "ff_norm", and "side".  Option: alpha.
     Nothing is left pending: the block returns None.

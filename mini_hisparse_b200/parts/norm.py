@@ -33,7 +33,7 @@ class RMSNorm(Norm):
 
     def forward_post(self, x, ctx: StepContext, delta: Product | None, alpha: float = 1.0, keep: float = 0.0,
                      name="x_copy"):
-        """Norm AFTER the sum, in place: x <- keep * x + rms(alpha * x + delta) * weight (float32).
+        """Post-norm, in place: x <- keep * x + rms(alpha * x + delta) * weight (float32).
         Returns the new rows in the compute dtype (x itself when that is float32): what the next
         product reads, since nothing normalises the stream again before it."""
         copy = None if ctx.rt.dtype == torch.float32 else ctx.ws.get(name, tuple(x.shape), ctx.rt.dtype)

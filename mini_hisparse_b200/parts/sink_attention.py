@@ -15,11 +15,12 @@ from .spec import PagedKVNeed, ParamSpec, PartSpec
 class SinkAttention(Mixer):
     """q = W_q h [q_heads x dim], k = W_k h [kv_heads x dim], v = W_v h [kv_heads x vdim], no biases.
 
-    * q and k are RMS-normalised over the WHOLE projection (all heads at once, before they are split
-      into heads; plain weights of that size), then rotated by the position part.
+    * q and k are each RMS-normalised as ONE vector spanning every head (the statistic is not per head; the
+      weight is a plain multiplier as long as that vector), and only then cut into heads and rotated by the
+      position part.
     * score = (q . k) * scale; a query at position i sees the keys at positions i - window + 1 ... i.
-    * The softmax's denominator has one more term, exp(sink_h): a learned number per query head that
-      has no key and no value and is not scaled.
+    * The softmax's denominator has one more term, exp(sink_h): a learned per-head logit that stands for no
+      position (it brings neither a key nor a value) and is used as stored, without the score scale.
     * The heads' outputs are multiplied by sigmoid(W_g h) and projected by W_o.
     * ``own_kv`` False: the layer has no k and v tensors; it reads the cache of another run entry
       (RunEntry.cache_of) with its own queries, window, sink and gate.
