@@ -27,7 +27,8 @@ def _top_k(value):
 
 def build_parser() -> argparse.ArgumentParser:
     parser = argparse.ArgumentParser(prog="mini_hisparse_b200",
-                                     description="Qwen2 generation on one B200 with hand-written kernels")
+                                     description="generation on one B200 with hand-written kernels (Qwen2 and Koronex model folders; "
+                                                 "--config configs/koronex-demo.json for a Koronex demo)")
     sub = parser.add_subparsers(dest="command", required=True)
     for name in ("demo", "generate", "bench"):
         c = sub.add_parser(name)

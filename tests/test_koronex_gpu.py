@@ -538,6 +538,21 @@ def test_greedy_generation_through_the_engine(models, dtype):
                 seq.append(tok)
 
 
+def test_command_line_demo_with_a_koronex_config(capsys):
+    """`demo --config configs/koronex-demo.json`: random weights, three requests through Engine and scheduler."""
+    from pathlib import Path
+
+    import mini_hisparse_b200
+    from mini_hisparse_b200 import cli
+
+    config = Path(mini_hisparse_b200.__file__).parent / "configs" / "koronex-demo.json"
+    assert cli.main(["demo", "--config", str(config), "--dtype", "bfloat16", "--requests", "3", "--prompt-tokens", "70",
+                     "--max-new-tokens", "6"]) == 0
+    report = json.loads(capsys.readouterr().out)
+    assert [r["generated_tokens"] for r in report["requests"].values()] == [6, 6, 6]
+    assert report["cache"]["state_groups"][0]["shape"] == [4, 32, 32]
+
+
 def test_trace_run_picks_the_model_by_its_config(models, tmp_path):
     """bin/trace_run on a Koronex folder: the same program, cache and step function as for every model."""
     folder, cfg, w = models["B"]
