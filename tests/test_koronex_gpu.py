@@ -457,6 +457,36 @@ def test_far_keys_and_key_splits_with_sink_and_gate(tmp_path, dtype):
         assert row_rms_error(got["r0"], whole["r0"]) < (F32_ROW if dtype == "float32" else BF16_CUT)
 
 
+EDGE_SHAPES = {
+    # no attention layer at all: no page group, only state slots
+    "lightning_only": dict(width=64, layers=[layer("lightning", light(2, 16, 16, [0.9, 0.99])),
+                                              layer("lightning", light(2, 16, 16, [0.5, 0.8]), ff=96)]),
+    # one layer, 32 query heads on one KV head (two chunks of 16 heads a tile), no feed-forward
+    "one_attention": dict(width=64, token_side=dict(dim=4), layers=[layer("attention", attn(32, 1, 16, 16, 50, 4))]),
+    # 20 heads on one KV head, keys and values 64 wide (tcgen05 and TMA tiles in bfloat16), whole heads rotated,
+    # a reader whose window is three times its owner's
+    "many_heads": dict(width=128, layers=[layer("attention", attn(20, 1, 64, 64, 300, 64, scale=0.12), ff=64),
+                                          layer("attention", attn(20, 1, 64, 64, 1000, 64, scale=0.12, kv_from=0))]),
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(EDGE_SHAPES))
+def test_shapes_at_the_edges(tmp_path, name, dtype):
+    from mini_hisparse_b200 import write_random_model
+
+    cfg = dict(architecture="Koronex", vocab=77, embedding=dict(scale=1.0), norm=dict(eps=1e-5), postln_alpha=1.2,
+               **EDGE_SHAPES[name])
+    write_random_model(cfg, 3, tmp_path, dtype=torch.bfloat16, matrix_std=0.15)
+    cfg, w = P.load_folder(tmp_path)
+    reqs = requests_for(cfg, [333, 1, 40, 150])
+    refs = {rid: P.forward(cfg, w, toks).float() for rid, toks in reqs.items()}
+    for steps in (S.mixed(reqs, seed=2), S.tail_one_by_one(reqs, tail=40)):
+        got, stats, pages = run_steps(tmp_path, dtype, steps)
+        check_against_plain(got, refs, dtype)
+    assert stats["graph_steps"] > 30
+
+
 def test_the_plain_model_is_sensitive_to_what_the_tests_are_for(models):
     """A window one key off, a sink left out, a reader that takes its own keys' layer for another, a decay
     state that is lost: each moves the plain model's logits by far more than the float32 tolerance, so the
