@@ -1,7 +1,9 @@
 // The tensor-core attention of attention_mma_kernel.cuh with the options that other mixers bring: keys
 // and values of different widths (any multiples of 8 up to 128; the tiles are padded to the next
-// multiple of 32), a sink per query head in the softmax's denominator, a gate on the output, and
-// softmax weights that keep 16 bits in the value product.  Work items, tile heights and the merge of
+// multiple of 32), a sink per query head in the softmax's denominator, a gate on the output (per element
+// or per head), softmax weights that keep 16 bits in the value product, several score maps per KV head
+// over shared values, capped scores, values that are the head of the key rows (a latent cache), and
+// float32 outputs.  Work items, tile heights and the merge of
 // key splits are those of attention_mma.cu.
 #include "attention_mma_kernel.cuh"
 
@@ -43,9 +45,13 @@ MHB_EXPORT int mhb_attention_mma_ext(const void* q, const void* cache, void* out
                                      const int* tok_part_row, const int* tok_nsplit, int* counters, int nq,
                                      int nkv, int d, int dv, int P, int num_pages, int window, float scale,
                                      const float* sink, const float* gate, int gate_nsplit,
-                                     long long gate_split_stride, int gate_ld, cudaStream_t stream) {
+                                     long long gate_split_stride, int gate_ld, int kparts, float softcap,
+                                     int shared_kv, int gate_per_head, int out_f32, cudaStream_t stream) {
     if (launch_items <= 0) return 0;
-    if (nkv <= 0 || nq % nkv) return fail("attention: %d query heads over %d KV heads", nq, nkv);
+    if (nkv <= 0 || kparts < 1 || nq % (nkv * kparts))
+        return fail("attention: %d query heads over %d KV heads with %d score maps each", nq, nkv, kparts);
+    if ((long long)nkv * kparts > 65535) return fail("attention: too many KV heads");
+    if (shared_kv && dv > kparts * d) return fail("attention: values %d wide cannot be the head of key rows %d wide", dv, kparts * d);
     if (!mhb_attention_mma_ext_supports(d, dv)) return fail("attention_mma_ext: widths %d and %d (multiples of 8 up to 128)", d, dv);
     if (!(scale > 0.f) && sink) return fail("attention_mma_ext: a sink needs a positive scale");
     AttnArgs a;
@@ -53,6 +59,7 @@ MHB_EXPORT int mhb_attention_mma_ext(const void* q, const void* cache, void* out
               tok_nsplit, counters, nq, nkv, P, num_pages, window, scale);
     a.d = d; a.dv = dv; a.sink = sink; a.gate = gate; a.gate_nsplit = gate_nsplit; a.gate_ld = gate_ld;
     a.gate_split_stride = (size_t)gate_split_stride;
+    a.kparts = kparts; a.softcap = softcap; a.shared_kv = shared_kv; a.gate_per_head = gate_per_head; a.out_f32 = out_f32;
     const int dp = (d + 31) / 32 * 32, dvp = (dv + 31) / 32 * 32;
     if (rows == 64) return dispatch_d<64>(dp, dvp, a, launch_items, stream);
     if (rows == 16) return dispatch_d<16>(dp, dvp, a, launch_items, stream);

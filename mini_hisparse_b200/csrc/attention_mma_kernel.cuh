@@ -51,7 +51,17 @@ struct AttnArgs {
     const float* gate;          // [gate_nsplit][T][gate_ld] or null
     int gate_nsplit, gate_ld;
     size_t gate_split_stride;
+    int kparts;                 // score maps per KV head: its key row holds kparts keys side by side, all over the same values
+    float softcap;              // s <- softcap * tanh(s / softcap) on the scaled score (0: none)
+    int shared_kv;              // the values are the first dv elements of the key rows; a page holds those rows only
+    int gate_per_head;          // the gate has one column per head instead of one per output element
+    int out_f32;                // `out` is float32 (a sum of the outputs is still to be taken in 32 bits)
 };
+
+__device__ __forceinline__ void store_out(const AttnArgs& a, size_t idx, float v) {
+    if (a.out_f32) ((float*)a.out)[idx] = v;
+    else a.out[idx] = __float2bfloat16_rn(v);
+}
 
 __device__ __forceinline__ float gate_of(const AttnArgs& a, int t, int col) {
     if (!a.gate) return 1.f;
@@ -82,7 +92,10 @@ struct Layout {
 // softmax's denominator (the running (max, sum) of ONE thread per row starts at (sink, 1), in the
 // unsplit item or in split 0 only), the output is multiplied by sigmoid(gate), and the softmax's
 // weights enter the value product as the sum of two bfloat16 numbers (the weight and what rounding
-// it lost), which keeps 16 bits of them instead of 8.
+// it lost), which keeps 16 bits of them instead of 8.  Further, with a.kparts > 1 every KV head has that many
+// score maps (gridDim.y = nkv * kparts; query head q belongs to map q % kparts; the maps' keys lie side by side
+// in the key row and share the values), a.softcap caps the scores, a.shared_kv takes the values from the head
+// of the key rows (a latent cache), a.gate_per_head reads one gate per head, a.out_f32 writes float32.
 template <int D, int DV, int ROWS, bool EXT>
 __global__ void __launch_bounds__(THREADS)
 attention_mma_kernel(const AttnArgs a) {
@@ -103,21 +116,27 @@ attention_mma_kernel(const AttnArgs a) {
     const int* it = a.items + (size_t)blockIdx.x * ITEM_INTS;
     const int seg = it[0], tok0 = it[1], ntok = it[2], head0 = it[3], nheads = it[4];
     const int kv_begin = it[5], kv_end = it[6], split = it[7];
-    const int kvh = blockIdx.y;
-    const int groups = a.nq / a.nkv;
+    const int kparts = EXT ? a.kparts : 1;
+    const int kvh = blockIdx.y / kparts, map = blockIdx.y - kvh * kparts;
+    const int groups = a.nq / (a.nkv * kparts);
     const int nrows = ntok * nheads;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // query head (as q, out and the partial buffers count them) of row r of this tile
+    auto head_of = [&](int r) { return (kvh * groups + head0 + r % nheads) * kparts + map; };
     const uint32_t q_s = (uint32_t)__cvta_generic_to_shared(smem);
     const uint32_t kv_s = q_s + L::Q_BYTES;       // [stage][K|V][KT][LD]
     const int* table = a.block_table + (size_t)seg * a.width;
-    const size_t page_elems = (size_t)a.nkv * a.P * (d_true + dv_true);
-    const size_t plane = (size_t)a.nkv * a.P * d_true;  // elements between the keys and the values of a page
+    const bool shared_kv = EXT && a.shared_kv;
+    const int k_ld = kparts * d_true;                    // a key row of one KV head: its maps side by side
+    const int v_ld = shared_kv ? k_ld : dv_true;
+    const size_t plane = shared_kv ? 0 : (size_t)a.nkv * a.P * k_ld;  // elements between the keys and the values of a page
+    const size_t page_elems = (size_t)a.nkv * a.P * k_ld + (shared_kv ? 0 : (size_t)a.nkv * a.P * dv_true);
 
     // ---- stage the queries --------------------------------------------------------------------
     for (int c = tid; c < ROWS * (D / 8); c += THREADS) {
         const int r = c / (D / 8), ch = c % (D / 8);
         const bool live = r < nrows;
-        const int t = tok0 + (live ? r / nheads : 0), h = kvh * groups + head0 + (live ? r % nheads : 0);
+        const int t = tok0 + (live ? r / nheads : 0), h = head_of(live ? r : 0);
         const __nv_bfloat16* src = a.q + ((size_t)t * a.nq + h) * d_true + (ch * 8 < d_true ? ch * 8 : 0);
         cp_async16(q_s + (r * LD + ch * 8) * 2, src, live && ch * 8 < d_true ? 16 : 0);
     }
@@ -145,12 +164,12 @@ attention_mma_kernel(const AttnArgs a) {
             int bytes = page >= 0 ? 16 : 0;
             if (ch < D / 8) {
                 if (ch * 8 >= d_true) bytes = 0;           // the tile's tail beyond the true width stays zero
-                if (bytes) src += (size_t)page * page_elems + ((size_t)kvh * a.P + within) * d_true + ch * 8;
+                if (bytes) src += (size_t)page * page_elems + ((size_t)kvh * a.P + within) * k_ld + map * d_true + ch * 8;
                 cp_async16(kbase + (j * LD + ch * 8) * 2, src, bytes);
             } else {
                 const int cv = ch - D / 8;
                 if (cv * 8 >= dv_true) bytes = 0;
-                if (bytes) src += (size_t)page * page_elems + plane + ((size_t)kvh * a.P + within) * dv_true + cv * 8;
+                if (bytes) src += (size_t)page * page_elems + plane + ((size_t)kvh * a.P + within) * v_ld + cv * 8;
                 cp_async16(vbase + (j * LDV + cv * 8) * 2, src, bytes);
             }
         }
@@ -180,7 +199,7 @@ attention_mma_kernel(const AttnArgs a) {
             for (int h = 0; h < 2; ++h) {
                 const int row = wrow + (lane >> 2) + 8 * h;
                 if (row < nrows) {
-                    m_run[h] = a.sink[kvh * groups + head0 + row % nheads] / a.scale;
+                    m_run[h] = a.sink[head_of(row)] / a.scale;
                     l_run[h] = (lane & 3) == 0 ? 1.f : 0.f;
                 }
             }
@@ -238,6 +257,15 @@ attention_mma_kernel(const AttnArgs a) {
             }
         }
 
+        if constexpr (EXT) {
+            if (a.softcap > 0.f) {      // the cap works on the scaled score; the tile stays in the raw products' units
+                const float to_cap = a.scale / a.softcap, from_cap = a.softcap / a.scale;
+#pragma unroll
+                for (int j = 0; j < NT; ++j)
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) s[j][x] = from_cap * tanhf(s[j][x] * to_cap);
+            }
+        }
         // ---- mask, online softmax -----------------------------------------------------------------
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -345,11 +373,15 @@ attention_mma_kernel(const AttnArgs a) {
                 acc += wgt * mg[(w * 16 + row) * MS + e];
                 lsum += wgt * mg[(w * 16 + row) * MS + DV + 1];
             }
-            const int t = tok0 + row / nheads, hq = kvh * groups + head0 + row % nheads;
+            const int t = tok0 + row / nheads, hq = head_of(row);
             if (split < 0) {
                 float res = lsum > 0.f ? acc / lsum : 0.f;
-                if constexpr (EXT) res *= gate_of(a, t, hq * dv_true + e);
-                a.out[((size_t)t * a.nq + hq) * dv_true + e] = __float2bfloat16_rn(res);
+                if constexpr (EXT) {
+                    res *= gate_of(a, t, a.gate_per_head ? hq : hq * dv_true + e);
+                    store_out(a, ((size_t)t * a.nq + hq) * dv_true + e, res);
+                } else {
+                    a.out[((size_t)t * a.nq + hq) * dv_true + e] = __float2bfloat16_rn(res);
+                }
             } else {
                 const size_t prow = (size_t)a.tok_part_row[t] + split;
                 a.part_acc[(prow * a.nq + hq) * dv_true + e] = acc;
@@ -366,7 +398,7 @@ attention_mma_kernel(const AttnArgs a) {
             __syncthreads();
             if (tid == 0) {
                 const int chunks = (groups + 15) / 16;
-                int* counter = a.counters + ((size_t)tok0 * a.nkv + kvh) * chunks + head0 / 16;
+                int* counter = a.counters + ((size_t)tok0 * gridDim.y + blockIdx.y) * chunks + head0 / 16;
                 const int ns = a.tok_nsplit[tok0];
                 const int prev = atomicAdd(counter, 1);
                 is_last = prev == ns - 1;
@@ -380,7 +412,7 @@ attention_mma_kernel(const AttnArgs a) {
                 __shared__ float inv_s[16];
                 const int ns = min(a.tok_nsplit[tok0], MAX_MERGE_SPLITS);
                 if (tid < nrows) {
-                    const int t = tok0 + tid / nheads, hq = kvh * groups + head0 + tid % nheads;
+                    const int t = tok0 + tid / nheads, hq = head_of(tid);
                     const size_t row0 = a.tok_part_row[t];
                     float M = -INFINITY;
                     for (int sp = 0; sp < ns; ++sp) M = fmaxf(M, __ldcg(a.part_ml + ((row0 + sp) * a.nq + hq) * 2));
@@ -396,15 +428,19 @@ attention_mma_kernel(const AttnArgs a) {
                 __syncthreads();
                 for (int idx = tid; idx < nrows * dv_true; idx += THREADS) {
                     const int row = idx / dv_true, e = idx - row * dv_true;
-                    const int t = tok0 + row / nheads, hq = kvh * groups + head0 + row % nheads;
+                    const int t = tok0 + row / nheads, hq = head_of(row);
                     const float* src = a.part_acc + ((size_t)a.tok_part_row[t] * a.nq + hq) * dv_true + e;
                     const size_t step = (size_t)a.nq * dv_true;
                     float acc = 0.f;
 #pragma unroll 4
                     for (int sp = 0; sp < ns; ++sp) acc += wgt_s[row][sp] * __ldcg(src + sp * step);
                     acc *= inv_s[row];
-                    if constexpr (EXT) acc *= gate_of(a, t, hq * dv_true + e);
-                    a.out[((size_t)t * a.nq + hq) * dv_true + e] = __float2bfloat16_rn(acc);
+                    if constexpr (EXT) {
+                        acc *= gate_of(a, t, a.gate_per_head ? hq : hq * dv_true + e);
+                        store_out(a, ((size_t)t * a.nq + hq) * dv_true + e, acc);
+                    } else {
+                        a.out[((size_t)t * a.nq + hq) * dv_true + e] = __float2bfloat16_rn(acc);
+                    }
                 }
             }
         }
@@ -413,17 +449,26 @@ attention_mma_kernel(const AttnArgs a) {
         for (int h = 0; h < 2; ++h) {
             const int row = wrow + (lane >> 2) + 8 * h;
             if (row >= nrows) continue;
-            const int t = tok0 + row / nheads, hq = kvh * groups + head0 + row % nheads;
+            const int t = tok0 + row / nheads, hq = head_of(row);
             if (split < 0) {
                 const float inv = l_run[h] > 0.f ? 1.f / l_run[h] : 0.f;
-                __nv_bfloat16* dst = a.out + ((size_t)t * a.nq + hq) * dv_true + (lane & 3) * 2;
+                const size_t o0 = ((size_t)t * a.nq + hq) * dv_true + (lane & 3) * 2;
+                __nv_bfloat16* dst = a.out + o0;
+                float gh = 1.f;
+                if constexpr (EXT) { if (a.gate_per_head) gh = gate_of(a, t, hq); }
 #pragma unroll
                 for (int i = 0; i < DTILES; ++i) {
                     if (EXT && i * 8 >= dv_true) break;
-                    float g0 = 1.f, g1 = 1.f;
+                    float g0 = gh, g1 = gh;
                     if constexpr (EXT) {
-                        g0 = gate_of(a, t, hq * dv_true + i * 8 + (lane & 3) * 2);
-                        g1 = gate_of(a, t, hq * dv_true + i * 8 + (lane & 3) * 2 + 1);
+                        if (!a.gate_per_head) {
+                            g0 = gate_of(a, t, hq * dv_true + i * 8 + (lane & 3) * 2);
+                            g1 = gate_of(a, t, hq * dv_true + i * 8 + (lane & 3) * 2 + 1);
+                        }
+                        if (a.out_f32) {
+                            *(float2*)((float*)a.out + o0 + i * 8) = make_float2(o[i][2 * h] * inv * g0, o[i][2 * h + 1] * inv * g1);
+                            continue;
+                        }
                     }
                     *(uint32_t*)(dst + i * 8) = pack_bf16(o[i][2 * h] * inv * g0, o[i][2 * h + 1] * inv * g1);
                 }
@@ -458,7 +503,7 @@ int launch(const AttnArgs& a, int launch_items, cudaStream_t stream) {
         cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         configured = true;
     }
-    dim3 grid(launch_items, a.nkv);
+    dim3 grid(launch_items, a.nkv * (EXT ? a.kparts : 1));
     launch_kernel(kern, grid, dim3(THREADS), smem, stream, a);
     return check_launch("attention_mma");
 }
@@ -475,5 +520,6 @@ inline void fill_args(AttnArgs& a, const void* q, const void* cache, void* out, 
     a.page_shift = -1;
     if (P > 0 && (P & (P - 1)) == 0) { a.page_shift = 0; while ((1 << a.page_shift) < P) ++a.page_shift; }
     a.d = a.dv = 0; a.sink = nullptr; a.gate = nullptr; a.gate_nsplit = 1; a.gate_ld = 0; a.gate_split_stride = 0;
+    a.kparts = 1; a.softcap = 0.f; a.shared_kv = 0; a.gate_per_head = 0; a.out_f32 = 0;
 }
 }  // namespace mhb_amma

@@ -21,7 +21,14 @@
 //              that stands for no position: the running (max, sum) starts at (sink_h, 1) instead of
 //              (-inf, 0), in the unsplit item or in split 0 only, so a token's parts hold it a single time
 //   gate       the output row is multiplied by sigmoid(gate[t][h * dv + e]); the gate comes as the
-//              columns of a float32 product (split-K parts summed in order)
+//              columns of a float32 product (split-K parts summed in order); with gate_per_head the
+//              gate is one number per head, gate[t][h]
+//   kparts     every KV head's key row holds `kparts` keys of width d side by side, each a score map of
+//              its own over the SAME values: query head q belongs to map q % kparts of KV head
+//              (q / kparts) / groups, and gridDim.y = nkv * kparts (one CTA per item, KV head and map)
+//   softcap    s <- softcap * tanh(s / softcap) on the scaled score, before the mask and the softmax
+//   shared_kv  the values ARE the first dv elements of the key rows (a latent cache: one row per
+//              position serves as key and as value), so a page holds [nkv][P][kparts * d] and nothing else
 #include "common.cuh"
 
 using namespace mhb;
@@ -52,6 +59,11 @@ struct AttnArgs {
     const float* gate;         // [gate_nsplit][T][gate_ld] or null
     int gate_nsplit, gate_ld;
     size_t gate_split_stride;
+    int kparts;                // score maps per KV head (1 unless the mixer says otherwise)
+    float softcap;             // 0: none
+    int shared_kv;             // values are the head of the key rows
+    int gate_per_head;         // the gate has one column per head
+    int out_f32;               // `out` is float32 whatever the dtype of q and the cache (a sum is still to come)
 };
 
 __device__ __forceinline__ float gate_of(const AttnArgs& a, int t, int col) {
@@ -78,10 +90,15 @@ attention_simt_kernel(const AttnArgs a) {
     const int* it = a.items + (size_t)blockIdx.x * ITEM_INTS;
     const int seg = it[0], tok0 = it[1], ntok = it[2], head0 = it[3], nheads = it[4];
     const int kv_begin = it[5], kv_end = it[6], split = it[7];
-    const int kvh = blockIdx.y;
-    const int groups = a.nq / a.nkv;
+    const int kparts = a.kparts;
+    const int kvh = blockIdx.y / kparts, map = blockIdx.y - kvh * kparts;
+    const int groups = a.nq / (a.nkv * kparts);
     const int nrows = ntok * nheads;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int k_ld = kparts * d;                                   // a key row of one KV head
+    const int v_ld = a.shared_kv ? k_ld : dv;
+    const size_t v_plane = a.shared_kv ? 0 : (size_t)a.nkv * a.P * k_ld;
+    const size_t page_elems = (size_t)a.nkv * a.P * k_ld + (a.shared_kv ? 0 : (size_t)a.nkv * a.P * dv);
     const CT* q = (const CT*)a.q;
     const CT* cache = (const CT*)a.cache;
 
@@ -90,7 +107,7 @@ attention_simt_kernel(const AttnArgs a) {
         const int r = idx / d, e = idx - r * d;
         float v = 0.f;
         if (r < nrows) {
-            const int t = tok0 + r / nheads, h = kvh * groups + head0 + r % nheads;
+            const int t = tok0 + r / nheads, h = (kvh * groups + head0 + r % nheads) * kparts + map;
             v = to_float(q[((size_t)t * a.nq + h) * d + e]);
         }
         q_s[idx] = v;
@@ -110,7 +127,7 @@ attention_simt_kernel(const AttnArgs a) {
         for (int i = 0; i < DPL; ++i) acc[rs][i] = 0.f;
         const int r = rs * WARPS + warp;
         if (a.sink && split <= 0 && r < nrows) {      // a single time per token: here or in split 0
-            m[rs] = a.sink[kvh * groups + head0 + r % nheads];
+            m[rs] = a.sink[(kvh * groups + head0 + r % nheads) * kparts + map];
             l[rs] = 1.f;
         }
     }
@@ -126,9 +143,9 @@ attention_simt_kernel(const AttnArgs a) {
                 if (page >= a.num_pages) page = -1;
             }
             if (page >= 0) {
-                const size_t pbase = (size_t)page * a.nkv * a.P * (d + dv);
-                const size_t off = pbase + ((size_t)kvh * a.P + kp % a.P) * d;
-                const size_t voff = pbase + (size_t)a.nkv * a.P * d + ((size_t)kvh * a.P + kp % a.P) * dv;
+                const size_t pbase = (size_t)page * page_elems;
+                const size_t off = pbase + ((size_t)kvh * a.P + kp % a.P) * k_ld + map * d;
+                const size_t voff = pbase + v_plane + ((size_t)kvh * a.P + kp % a.P) * v_ld;
                 for (int e = lane; e < d; e += 32) k_s[j * (d + 1) + e] = to_float(cache[off + e]);
                 for (int e = lane; e < dv; e += 32) v_s[j * dv + e] = to_float(cache[voff + e]);
             } else {
@@ -148,6 +165,7 @@ attention_simt_kernel(const AttnArgs a) {
             float s = 0.f;
             for (int e = 0; e < d; ++e) s = fmaf(qr[e], kr[e], s);
             s *= a.scale;
+            if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
             const bool valid = kp < kv_end && kp <= qp && (a.window <= 0 || kp > qp - a.window);
             if (!valid) s = -INFINITY;
             const float m_new = fmaxf(m[rs], warp_max(s));
@@ -176,14 +194,17 @@ attention_simt_kernel(const AttnArgs a) {
     for (int rs = 0; rs < ROWS_PER_WARP; ++rs) {
         const int r = rs * WARPS + warp;
         if (r >= nrows) continue;
-        const int t = tok0 + r / nheads, h = kvh * groups + head0 + r % nheads;
+        const int t = tok0 + r / nheads, h = (kvh * groups + head0 + r % nheads) * kparts + map;
         if (split < 0) {
             const float inv = l[rs] > 0.f ? 1.f / l[rs] : 0.f;
-            CT* o = (CT*)a.out + ((size_t)t * a.nq + h) * dv;
+            const size_t o0 = ((size_t)t * a.nq + h) * dv;
 #pragma unroll
             for (int i = 0; i < DPL; ++i) {
                 const int e = lane + 32 * i;
-                if (e < dv) o[e] = from_float<CT>(acc[rs][i] * inv * gate_of(a, t, h * dv + e));
+                if (e >= dv) continue;
+                const float val = acc[rs][i] * inv * gate_of(a, t, a.gate_per_head ? h : h * dv + e);
+                if (a.out_f32) ((float*)a.out)[o0 + e] = val;
+                else ((CT*)a.out)[o0 + e] = from_float<CT>(val);
             }
         } else {
             const size_t prow = (size_t)a.tok_part_row[t] + split;
@@ -209,7 +230,8 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_acc,
                                          const int* __restrict__ tok_part_row,
                                          const int* __restrict__ tok_nsplit, OT* __restrict__ out,
                                          int nq, int d, int every, const float* __restrict__ gate,
-                                         int gate_nsplit, size_t gate_split_stride, int gate_ld) {
+                                         int gate_nsplit, size_t gate_split_stride, int gate_ld,
+                                         int gate_per_head) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x, h = blockIdx.y;
@@ -235,7 +257,7 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_acc,
         }
         float g = 1.f;
         if (gate) {
-            const size_t idx = (size_t)t * gate_ld + h * d + e;
+            const size_t idx = (size_t)t * gate_ld + (gate_per_head ? h : h * d + e);
             float z = gate[idx];
             for (int s = 1; s < gate_nsplit; ++s) z += gate[idx + (size_t)s * gate_split_stride];
             g = 1.f / (1.f + expf(-z));
@@ -248,7 +270,7 @@ template <typename CT>
 int launch_attention(const AttnArgs& a, int max_items, cudaStream_t stream) {
     const int dpl = (a.dv + 31) / 32;
     const size_t smem = sizeof(float) * ((size_t)R_TILE * a.d + (size_t)KT * (a.d + 1) + (size_t)KT * a.dv);
-    dim3 grid(max_items, a.nkv);
+    dim3 grid(max_items, a.nkv * a.kparts);
 #define MHB_ATTN_CASE(N)                                                                        \
     case N: {                                                                                   \
         auto kern = attention_simt_kernel<CT, N>;                                               \
@@ -285,6 +307,7 @@ MHB_EXPORT int mhb_attention_simt(const void* q, const void* cache, void* out, i
     a.tok_part_row = tok_part_row; a.num_items = num_items; a.width = width; a.nq = nq;
     a.nkv = nkv; a.d = d; a.P = P; a.num_pages = num_pages; a.window = window; a.scale = scale;
     a.dv = d; a.sink = nullptr; a.gate = nullptr; a.gate_nsplit = 1; a.gate_ld = 0; a.gate_split_stride = 0;
+    a.kparts = 1; a.softcap = 0.f; a.shared_kv = 0; a.gate_per_head = 0; a.out_f32 = 0;
     MHB_DISPATCH_DTYPE(dtype, CT, return launch_attention<CT>(a, max_items, stream));
     return 0;
 }
@@ -296,8 +319,12 @@ MHB_EXPORT int mhb_attention_simt_ext(const void* q, const void* cache, void* ou
                                       int width, const int* tok_part_row, int nq, int nkv, int d, int dv, int P,
                                       int num_pages, int window, float scale, const float* sink,
                                       const float* gate, int gate_nsplit, long long gate_split_stride, int gate_ld,
+                                      int kparts, float softcap, int shared_kv, int gate_per_head, int out_f32,
                                       cudaStream_t stream) {
     if (max_items <= 0) return 0;
+    if (kparts < 1 || nq % (nkv > 0 ? nkv * kparts : 1)) return fail("attention: %d query heads over %d KV heads with %d score maps each", nq, nkv, kparts);
+    if ((long long)nkv * kparts > 65535) return fail("attention: too many KV heads");
+    if (shared_kv && dv > kparts * d) return fail("attention: values %d wide cannot be the head of key rows %d wide", dv, kparts * d);
     if (nkv <= 0 || nq % nkv) return fail("attention: %d query heads over %d KV heads", nq, nkv);
     if (nkv > 65535) return fail("attention: too many KV heads");
     if (d > 1024) return fail("attention: a key width of %d is larger than 1024", d);
@@ -308,6 +335,8 @@ MHB_EXPORT int mhb_attention_simt_ext(const void* q, const void* cache, void* ou
     a.nkv = nkv; a.d = d; a.P = P; a.num_pages = num_pages; a.window = window; a.scale = scale;
     a.dv = dv; a.sink = sink; a.gate = gate; a.gate_nsplit = gate_nsplit; a.gate_ld = gate_ld;
     a.gate_split_stride = (size_t)gate_split_stride;
+    a.kparts = kparts; a.softcap = softcap; a.shared_kv = shared_kv; a.gate_per_head = gate_per_head;
+    a.out_f32 = out_f32;
     MHB_DISPATCH_DTYPE(dtype, CT, return launch_attention<CT>(a, max_items, stream));
     return 0;
 }
@@ -323,7 +352,7 @@ MHB_EXPORT int mhb_attention_combine(const float* part_acc, const float* part_ml
     const int threads = d >= 128 ? 128 : 32 * ((d + 31) / 32);
     MHB_DISPATCH_DTYPE(dtype, OT,
         launch_kernel(attention_combine_kernel<OT>, grid, dim3(threads), 0, stream, part_acc, part_ml,
-                      tok_part_row, tok_nsplit, (OT*)out, nq, d, every, (const float*)nullptr, 1, (size_t)0, 0));
+                      tok_part_row, tok_nsplit, (OT*)out, nq, d, every, (const float*)nullptr, 1, (size_t)0, 0, 0));
     return check_launch("attention_combine");
 }
 
@@ -331,7 +360,8 @@ MHB_EXPORT int mhb_attention_combine(const float* part_acc, const float* part_ml
 MHB_EXPORT int mhb_attention_combine_gated(const float* part_acc, const float* part_ml, const int* tok_part_row,
                                            const int* tok_nsplit, void* out, int dtype, int T, int nq, int d,
                                            int every, const float* gate, int gate_nsplit,
-                                           long long gate_split_stride, int gate_ld, cudaStream_t stream) {
+                                           long long gate_split_stride, int gate_ld, int gate_per_head,
+                                           cudaStream_t stream) {
     if (T <= 0) return 0;
     if (every <= 0 && (!tok_part_row || !tok_nsplit)) return fail("attention_combine: no list of parts");
     dim3 grid(T, nq);
@@ -339,6 +369,6 @@ MHB_EXPORT int mhb_attention_combine_gated(const float* part_acc, const float* p
     MHB_DISPATCH_DTYPE(dtype, OT,
         launch_kernel(attention_combine_kernel<OT>, grid, dim3(threads), 0, stream, part_acc, part_ml,
                       tok_part_row, tok_nsplit, (OT*)out, nq, d, every, gate, gate_nsplit,
-                      (size_t)gate_split_stride, gate_ld));
+                      (size_t)gate_split_stride, gate_ld, gate_per_head));
     return check_launch("attention_combine");
 }

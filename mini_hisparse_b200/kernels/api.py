@@ -429,22 +429,29 @@ def gemm_tc_qkv_rope(x, w, bias, cos_sin, positions, tok_seg, block_table, q_out
 
 def attention_simt(q, cache, out, part_acc, part_ml, items, num_items, max_items, positions,
                    block_table, tok_part_row, *, nq, nkv, d, page_size, window=0, scale=None, dv=None,
-                   sink=None, gate=None, gate_nsplit=1, gate_split_stride=0):
+                   sink=None, gate=None, gate_nsplit=1, gate_split_stride=0, kparts=1, softcap=0.0,
+                   shared_kv=False, gate_per_head=False):
     """CUDA-core attention over the items of a plan.  Options: ``dv`` values of another width than the
     keys (a page then holds the keys of all KV heads followed by their values), ``sink`` float32 [nq]
     (one extra term exp(sink_h) in the softmax's denominator), ``gate`` (the output is multiplied by its
-    sigmoid; columns of a float32 product)."""
+    sigmoid; columns of a float32 product; ``gate_per_head``: one column per head), ``kparts`` score maps
+    per KV head (its key row holds kparts keys side by side; ``nq`` counts every map of every head),
+    ``softcap`` (s <- softcap tanh(s / softcap)), ``shared_kv`` (the values are the first dv elements of
+    the key rows, and a page holds nothing but those rows)."""
     lib = build.load("attention_simt")
     if scale is None:
         scale = float(d) ** -0.5
-    if dv is not None or sink is not None or gate is not None:
+    general = kparts != 1 or softcap or shared_kv or gate_per_head or out.dtype != q.dtype
+    if dv is not None or sink is not None or gate is not None or general:
         g = _gate_args(gate, gate_nsplit, gate_split_stride)
         _check(lib, lib.mhb_attention_simt_ext(
             _ptr(q), _ptr(cache), _ptr(out), c_int(dtype_code(q.dtype)), _ptr(part_acc), _ptr(part_ml),
             _ptr(items), c_int(num_items), c_int(max_items), _ptr(positions), _ptr(block_table),
             c_int(block_table.shape[-1]), _ptr(tok_part_row), c_int(nq), c_int(nkv), c_int(d), c_int(dv or d),
             c_int(page_size), c_int(cache.shape[0]), c_int(window or 0), c_float(scale), _ptr(sink),
-            g[0], g[1], g[2], g[3], _stream()), "attention")
+            g[0], g[1], g[2], g[3], c_int(kparts), c_float(softcap or 0.0), c_int(1 if shared_kv else 0),
+            c_int(1 if gate_per_head else 0), c_int(1 if out.dtype == torch.float32 else 0), _stream()),
+            "attention")
         return
     _check(lib, lib.mhb_attention_simt(
         _ptr(q), _ptr(cache), _ptr(out), c_int(dtype_code(q.dtype)), _ptr(part_acc), _ptr(part_ml),
@@ -501,6 +508,9 @@ def lightning_chunked_tc(proj, q0, k0, v0, decay, state, out, tok_seg, seg_slot,
            "lightning_chunked_tc")
 
 
+MMA_EXT_GENERAL = True      # the tensor-core attention takes score maps, a cap, shared rows and float32 outputs
+
+
 def attention_mma_ext_supports(d: int, dv: int) -> bool:
     """Widths of keys and values the tensor-core attention with options takes (tiles padded to multiples of 32)."""
     return 8 <= d <= 128 and d % 8 == 0 and 8 <= dv <= 128 and dv % 8 == 0
@@ -508,13 +518,17 @@ def attention_mma_ext_supports(d: int, dv: int) -> bool:
 
 def attention_mma_ext(q, cache, out, part_acc, part_ml, items, num_items, rows, positions, block_table,
                       tok_part_row, *, nq, nkv, d, dv, page_size, window=0, scale=None, tok_nsplit=None,
-                      counters=None, sink=None, gate=None, gate_nsplit=1, gate_split_stride=0):
+                      counters=None, sink=None, gate=None, gate_nsplit=1, gate_split_stride=0, kparts=1, softcap=0.0,
+                      shared_kv=False, gate_per_head=False):
     """attention_mma with the options of attention_simt: values ``dv`` wide in pages that hold the keys of
     all KV heads followed by their values, a ``sink`` per query head, a ``gate`` on the output; the softmax's
-    weights enter the value product as two bfloat16 numbers each (16 bits instead of 8)."""
+    weights enter the value product as two bfloat16 numbers each (16 bits instead of 8).  ``kparts``,
+    ``softcap``, ``shared_kv`` and ``gate_per_head`` as in attention_simt; ``out`` may be float32."""
     lib = build.load("attention_mma_ext")
     if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or not cache.is_contiguous():
         raise KernelError("attention_mma_ext: q and the (contiguous) pool must be bfloat16")
+    if out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError("attention_mma_ext: the output must be bfloat16 or float32")
     if scale is None:
         scale = float(d) ** -0.5
     g = _gate_args(gate, gate_nsplit, gate_split_stride)
@@ -523,7 +537,9 @@ def attention_mma_ext(q, cache, out, part_acc, part_ml, items, num_items, rows, 
         c_int(num_items), c_int(rows), _ptr(positions), _ptr(block_table), c_int(block_table.shape[-1]),
         _ptr(tok_part_row), _ptr(tok_nsplit), _ptr(counters), c_int(nq), c_int(nkv), c_int(d), c_int(dv),
         c_int(page_size), c_int(cache.shape[0]), c_int(window or 0), c_float(scale), _ptr(sink),
-        g[0], g[1], g[2], g[3], _stream()), "attention_mma_ext")
+        g[0], g[1], g[2], g[3], c_int(kparts), c_float(softcap or 0.0), c_int(1 if shared_kv else 0),
+        c_int(1 if gate_per_head else 0), c_int(1 if out.dtype == torch.float32 else 0), _stream()),
+        "attention_mma_ext")
 
 
 def attention_tma_supports(d: int, page_size: int) -> bool:
@@ -670,7 +686,7 @@ def attention_tc_ext(q, cache, out, items, num_items, positions, block_table, *,
 
 
 def attention_combine(part_acc, part_ml, tok_part_row, tok_nsplit, out, *, nq, d, every=0, gate=None,
-                      gate_nsplit=1, gate_split_stride=0):
+                      gate_nsplit=1, gate_split_stride=0, gate_per_head=False):
     """Merge the parts of every token's attention.  ``every`` > 0: each token has exactly that many parts,
     in the rows t * every ... of the partial buffers (the two index arrays may be None).  ``d`` is the
     width of a head's output; ``gate``: see attention_simt."""
@@ -681,7 +697,8 @@ def attention_combine(part_acc, part_ml, tok_part_row, tok_nsplit, out, *, nq, d
         _check(lib, lib.mhb_attention_combine_gated(_ptr(part_acc), _ptr(part_ml), _ptr(tok_part_row),
                                                     _ptr(tok_nsplit), _ptr(out), c_int(dtype_code(out.dtype)),
                                                     c_int(T), c_int(nq), c_int(d), c_int(every), g[0], g[1], g[2],
-                                                    g[3], _stream()), "attention_combine")
+                                                    g[3], c_int(1 if gate_per_head else 0), _stream()),
+               "attention_combine")
         return
     _check(lib, lib.mhb_attention_combine(_ptr(part_acc), _ptr(part_ml), _ptr(tok_part_row),
                                           _ptr(tok_nsplit), _ptr(out), c_int(dtype_code(out.dtype)),
@@ -698,3 +715,132 @@ def sample(logits, temperature, seed, counter, out):
     _check(lib, lib.mhb_sample(_ptr(logits), c_longlong(logits.stride(0)), c_int(R), c_int(V),
                                _ptr(temperature), _ptr(seed), _ptr(counter), _ptr(out), _stream()),
            "sample")
+
+
+# ---- parts of parallel blocks, multi-map attention and latent attention (csrc/mixparts.cu) --------------
+def _delta_args(delta):
+    """(pointer, parts, stride between parts) of a pending product (None: nothing to add)."""
+    if delta is None:
+        return c_void_p(0), c_int(1), c_longlong(0)
+    return _ptr(delta.tensor), c_int(delta.nsplit), c_longlong(delta.split_stride)
+
+
+def _delta_dtype(*deltas) -> int:
+    kinds = {d.tensor.dtype for d in deltas if d is not None}
+    if len(kinds) > 1:
+        raise KernelError("products that are added together must have one dtype")
+    return dtype_code(kinds.pop()) if kinds else F32
+
+
+def add_layernorm(x, weight, eps, out, delta=None, delta2=None, rows=None):
+    """out[r] = layernorm(x[s] + delta[s] + delta2[s]) * weight (no bias) with s = rows[r] if rows is given
+    else r; without ``rows`` and with a delta the sum is written back to ``x``.  The deltas are products
+    (objects with tensor, nsplit, split_stride), each possibly float32 split-K parts."""
+    lib = build.load("mixparts")
+    R, H = out.shape
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("add_layernorm: the stream must be a contiguous float32 matrix")
+    if delta is None and delta2 is not None:
+        delta, delta2 = delta2, None
+    a, b = _delta_args(delta), _delta_args(delta2)
+    _check(lib, lib.mhb_add_layernorm(_ptr(x), a[0], a[1], a[2], b[0], b[1], b[2], c_int(_delta_dtype(delta, delta2)),
+                                      _ptr(weight), c_float(eps), _ptr(rows), _ptr(out), c_int(dtype_code(out.dtype)),
+                                      c_int(R), c_int(H), _stream()), "add_layernorm")
+
+
+def stream_pack(x, dst, col0: int, delta=None, delta2=None, zero: bool = False):
+    """dst[:, col0 : col0 + W] = x + delta + delta2 in dst's dtype (x float32 [T, W]); with ``zero`` the
+    stream is left at zero (whoever replaces the stream by a product adds that product into it)."""
+    lib = build.load("mixparts")
+    T, W = x.shape
+    if x.dtype != torch.float32 or not x.is_contiguous() or dst.stride(1) != 1:
+        raise KernelError("stream_pack: the stream must be contiguous float32, the target's rows contiguous")
+    if delta is None and delta2 is not None:
+        delta, delta2 = delta2, None
+    a, b = _delta_args(delta), _delta_args(delta2)
+    _check(lib, lib.mhb_stream_pack(_ptr(x), a[0], a[1], a[2], b[0], b[1], b[2], c_int(_delta_dtype(delta, delta2)),
+                                    _ptr(dst), c_int(dtype_code(dst.dtype)), c_int(dst.stride(0)), c_int(col0),
+                                    c_int(T), c_int(W), c_int(1 if zero else 0), _stream()), "stream_pack")
+
+
+GLU_ACTS = {"silu": 0, "gelu_tanh": 1}
+
+
+def glu_act(gate_up, out, act: str, nsplit=1, split_stride=0, block=None):
+    """out[t, i] = act(gate_i) * up_i; gate_up[t] holds blocks of ``block`` gate values followed by the up
+    values of the same indices (default: one block, [gate | up])."""
+    lib = build.load("mixparts")
+    T, I = out.shape
+    _check(lib, lib.mhb_glu_act(_ptr(gate_up), c_int(dtype_code(gate_up.dtype)), c_int(nsplit), c_longlong(split_stride),
+                                _ptr(out), c_int(dtype_code(out.dtype)), c_int(T), c_int(I), c_int(block or I),
+                                c_int(GLU_ACTS[act]), _stream()), "glu_act")
+
+
+def rope_append_maps(proj, positions, tok_seg, block_table, inv_freq, rotary_dim, interleaved, q_out, cache, *,
+                     nq, nkv, kparts, d, dv, page_size, nsplit=1, split_stride=0, status=None):
+    """Rows of the float32 product [q: nq * d | k: nkv * kparts * d | v: nkv * dv | ...]: the first
+    ``rotary_dim`` elements of every q and k map are rotated, q goes to ``q_out`` [T, nq * d], keys and values
+    into the page of the position ([keys: nkv][P][kparts * d] then [values: nkv][P][dv])."""
+    lib = build.load("mixparts")
+    T = q_out.shape[0]
+    if proj.dtype != torch.float32 or cache.dtype != q_out.dtype:
+        raise KernelError("rope_append_maps: a float32 product; cache and q of one dtype")
+    if rotary_dim and (inv_freq is None or inv_freq.numel() != rotary_dim // 2):
+        raise KernelError(f"rope_append_maps: {rotary_dim} rotated elements need {rotary_dim // 2} frequencies")
+    _check(lib, lib.mhb_rope_append_maps(
+        _ptr(proj), c_int(nsplit), c_longlong(split_stride), c_int(proj.stride(-2)), _ptr(positions), _ptr(tok_seg),
+        _ptr(block_table), c_int(block_table.shape[-1]), _ptr(inv_freq), c_int(rotary_dim or 0),
+        c_int(1 if interleaved else 0), _ptr(q_out), _ptr(cache), c_int(dtype_code(q_out.dtype)), c_int(T), c_int(nq),
+        c_int(nkv), c_int(kparts), c_int(d), c_int(dv), c_int(page_size), c_int(cache.shape[0]), _ptr(status),
+        _stream()), "rope_append_maps")
+
+
+def latent_prep(proj, weight, eps, positions, tok_seg, block_table, inv_freq, interleaved, q_plain, q_full, cache, *,
+                heads, d, dr, rank, page_size, write_kv=True, nsplit=1, split_stride=0, status=None):
+    """Rows of the float32 product [q: heads * (d + dr) | latent: rank | key part: dr | ...]: the latent is
+    divided by its root mean square and multiplied by ``weight``, the key part and the last dr elements of each
+    q head are rotated; the cache row [latent | key part] goes into the position's page ([P][rank + dr]),
+    q's unrotated parts to ``q_plain`` [T, heads, d], its rotated parts to the last dr columns of ``q_full``
+    [T, heads, rank + dr]."""
+    lib = build.load("mixparts")
+    T = q_plain.shape[0]
+    if proj.dtype != torch.float32 or cache.dtype != q_full.dtype or q_plain.dtype != q_full.dtype:
+        raise KernelError("latent_prep: a float32 product; cache and q of one dtype")
+    if dr and (inv_freq is None or inv_freq.numel() != dr // 2):
+        raise KernelError(f"latent_prep: {dr} rotated elements need {dr // 2} frequencies")
+    _check(lib, lib.mhb_latent_prep(
+        _ptr(proj), c_int(nsplit), c_longlong(split_stride), c_int(proj.stride(-2)), _ptr(weight), c_float(eps),
+        _ptr(positions), _ptr(tok_seg), _ptr(block_table), c_int(block_table.shape[-1]), _ptr(inv_freq),
+        c_int(1 if interleaved else 0), _ptr(q_plain), _ptr(q_full), _ptr(cache), c_int(dtype_code(q_full.dtype)),
+        c_int(T), c_int(heads), c_int(d), c_int(dr), c_int(rank), c_int(page_size), c_int(cache.shape[0]),
+        c_int(1 if write_kv else 0), _ptr(status), _stream()), "latent_prep")
+
+
+def head_linear(x, w, out):
+    """out[t, h, :] = w[h] @ x[t, h, :] with float32 accumulation: x [T, heads, K] and out [T, heads, N] may be
+    views with any token and head strides (last dimension contiguous), w [heads, N, K] contiguous."""
+    lib = build.load("mixparts")
+    T, H, Kd = x.shape
+    N = w.shape[1]
+    if tuple(w.shape) != (H, N, Kd) or tuple(out.shape) != (T, H, N):
+        raise KernelError(f"head_linear: x {list(x.shape)}, w {list(w.shape)}, out {list(out.shape)}")
+    if x.stride(2) != 1 or out.stride(2) != 1 or not w.is_contiguous():
+        raise KernelError("head_linear: the last dimensions must be contiguous")
+    _check(lib, lib.mhb_head_linear(_ptr(x), c_int(dtype_code(x.dtype)), c_longlong(x.stride(0)), c_longlong(x.stride(1)),
+                                    _ptr(w), c_int(dtype_code(w.dtype)), _ptr(out), c_int(dtype_code(out.dtype)),
+                                    c_longlong(out.stride(0)), c_longlong(out.stride(1)), c_int(T), c_int(H), c_int(N),
+                                    c_int(Kd), _stream()), "head_linear")
+
+
+def maps_combine(a, lam: float, eps: float, post: float, out, gate=None, gate_nsplit=1, gate_split_stride=0):
+    """a float32 [T, heads, 2, dv]: o = a[..., 0, :] - lam * a[..., 1, :], divided by its root mean square over
+    dv (eps inside the root), times ``post``, times sigmoid(gate[t, h]) (one column per head of a float32
+    product); out [T, heads * dv]."""
+    lib = build.load("mixparts")
+    T, H, two, dv = a.shape
+    if two != 2 or a.dtype != torch.float32 or not a.is_contiguous() or not out.is_contiguous():
+        raise KernelError("maps_combine: a must be contiguous float32 [T, heads, 2, dv]")
+    g = _gate_args(gate, gate_nsplit, gate_split_stride)
+    _check(lib, lib.mhb_maps_combine(_ptr(a), c_float(lam), c_float(eps), c_float(post), g[0], g[1], g[2], g[3],
+                                     _ptr(out), c_int(dtype_code(out.dtype)), c_int(T), c_int(H), c_int(dv),
+                                     _stream()), "maps_combine")

@@ -109,6 +109,8 @@ class DecoderModel:
         for i, entry in enumerate(self.spec.order):
             view = caches[i]
             block = self.blocks[entry.layer]
+            if entry.before is not None:       # a part of the model as a whole transforms the stream first
+                x, pending = self.shared[entry.before].forward_stream(x, pending, ctx)
             pending = block.forward(x, pending, ctx, view)
             if not block.keeps_copy:
                 ctx.extras.pop("x_copy", None)     # whoever changed the stream did not keep its copy in step
@@ -117,7 +119,7 @@ class DecoderModel:
         if observer is not None and pending is not None:
             # the hook's last call sees the finished residual stream (the head needs only its wanted
             # rows and never adds the last output into every row)
-            K.residual_add(x, pending.tensor, nsplit=pending.nsplit, split_stride=pending.split_stride)
+            pending.add_into(x)
             observer("final", x, None)
             pending = None
         if rows is None or rows.numel() == 0:

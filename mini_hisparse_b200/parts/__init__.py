@@ -1,5 +1,6 @@
 """Parts that layers are put together from.  Importing the package registers the built-in kinds."""
-from . import attention, block, embedding, feed_forward, lightning, norm, position, sink_attention  # noqa: F401
+from . import (attention, block, embedding, feed_forward, latent_attention, lightning, multimap_attention, norm,  # noqa: F401
+               position, sink_attention)
 from .base import (Block, CacheView, FeedForward, Mixer, Norm, Part, Product, Runtime, Segment, StepContext,
                    StepPlanner, Workspace)
 from .registry import (
@@ -16,5 +17,5 @@ from .registry import (
     register_norm,
     register_position,
 )
-from .spec import (CacheNeed, LayerSpec, ModelSpec, PagedKVNeed, PagedNeed, ParamSpec, PartSpec, RunEntry,
+from .spec import (CacheNeed, LayerSpec, ModelSpec, PagedKVNeed, PagedNeed, PagedRowsNeed, ParamSpec, PartSpec, RunEntry,
                    StateNeed)

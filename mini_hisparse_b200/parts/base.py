@@ -35,10 +35,13 @@ from .spec import CacheNeed, ParamSpec, PartSpec
 @dataclass
 class Product:
     """The result of a matrix product: one matrix, or ``nsplit`` float32 partial matrices
-    [nsplit, M, N] that the consumer sums in order (split-K)."""
+    [nsplit, M, N] that the consumer sums in order (split-K).  ``also``: a second product of the same
+    shape that is to be added wherever this one is (a block whose two sublayers both add to the
+    stream leaves both pending)."""
 
     tensor: torch.Tensor
     nsplit: int = 1
+    also: "Product | None" = None
 
     @property
     def split_stride(self) -> int:
@@ -52,7 +55,22 @@ class Product:
 
     def reduced(self) -> torch.Tensor:
         """The product as one float32 matrix (for inspection; the kernels sum the parts themselves)."""
-        return self.tensor.float().sum(0) if self.nsplit > 1 else self.tensor.float()
+        out = self.tensor.float().sum(0) if self.nsplit > 1 else self.tensor.float()
+        return out if self.also is None else out + self.also.reduced()
+
+    def add_into(self, x: torch.Tensor) -> None:
+        """x += this product (and what rides along), in float32."""
+        K.residual_add(x, self.tensor, nsplit=self.nsplit, split_stride=self.split_stride)
+        if self.also is not None:
+            self.also.add_into(x)
+
+    def settle_also(self, x: torch.Tensor) -> "Product":
+        """Add ``also`` into the float32 stream x now and return this product without it: for a
+        consumer whose kernel adds one product only."""
+        if self.also is None:
+            return self
+        self.also.add_into(x)
+        return Product(self.tensor, self.nsplit)
 
 
 class Workspace:
@@ -142,6 +160,18 @@ class Runtime:
         rotary_dim, inv_freq and interleaved): then q_out and the cache are written and True is
         returned.  False: the caller runs the product and the rotary kernel one after the other."""
         return False
+
+    def glu_layout(self, gate: torch.Tensor, up: torch.Tensor):
+        """swiglu_layout for a gate with any activation (see linear_glu)."""
+        return torch.cat((gate, up), 0).contiguous(), gate.shape[0]
+
+    def linear_glu(self, x, weight, block: int, activation: str, ws: Workspace, name: str) -> torch.Tensor:
+        """act(x Wg^T) * (x Wu^T) in the compute dtype for a weight from glu_layout(); the activation
+        ("silu", "gelu_tanh") is taken in float32 on the product's float32 output."""
+        gu = self.linear(x, weight, ws, name + "_gu", out_dtype=torch.float32)
+        out = ws.get(name, (x.shape[0], weight.shape[0] // 2), self.dtype)
+        K.glu_act(gu.tensor, out, activation, nsplit=gu.nsplit, split_stride=gu.split_stride, block=block)
+        return out
 
     def linear_swiglu(self, x, weight, block: int, ws: Workspace, name: str) -> torch.Tensor:
         """silu(x Wg^T) * (x Wu^T) in the compute dtype."""

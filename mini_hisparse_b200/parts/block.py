@@ -79,7 +79,7 @@ class PostNormBlock(Block):
 
     def forward(self, x, pending: Product | None, ctx: StepContext, cache: CacheView | None):
         if pending is not None:          # the block before this one was of another arrangement
-            K.residual_add(x, pending.tensor, nsplit=pending.nsplit, split_stride=pending.split_stride)
+            pending.add_into(x)
             ctx.extras.pop("x_copy", None)
         h = ctx.extras.get("x_copy")
         if h is None:
@@ -96,3 +96,33 @@ class PostNormBlock(Block):
             h = self.side.forward_into(x, h, ctx)
         ctx.extras["x_copy"] = h
         return None
+
+
+@register_block("parallel")
+class ParallelBlock(Block):
+    """One norm, both sublayers read its output:  h = norm(x);  x <- x + mixer(h) + ff(h).
+
+    Roles: "norm", "mixer", and optionally "feed_forward" (a layer without one adds the mixer alone).
+    Both outputs are left pending together (Product.also); the next norm adds them into the stream in
+    the same pass in which it normalises.
+    """
+
+    def __init__(self, spec: LayerSpec, rt):
+        self.spec = spec
+        self.norm = NORMS.build(spec.part("norm"), rt=rt)
+        self.mixer = MIXERS.build(spec.part("mixer"), rt=rt)
+        self.feed_forward = FEED_FORWARDS.build(spec.part("feed_forward"), rt=rt) if spec.has("feed_forward") else None
+
+    def parts(self):
+        out = {"norm": self.norm, "mixer": self.mixer}
+        if self.feed_forward is not None:
+            out["feed_forward"] = self.feed_forward
+        return out
+
+    def forward(self, x, pending: Product | None, ctx: StepContext, cache: CacheView | None) -> Product:
+        h = self.norm.forward(x, ctx, delta=pending)
+        a = self.mixer.forward(h, ctx, cache)
+        if self.feed_forward is None:
+            return a
+        f = self.feed_forward.forward(h, ctx)
+        return Product(a.tensor, a.nsplit, also=f)

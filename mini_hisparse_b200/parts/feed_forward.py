@@ -124,3 +124,41 @@ class TokenSide(FeedForward):
 
     def forward(self, h, ctx):
         raise NotImplementedError("a token_side part adds into the stream: call forward_into")
+
+
+@register_feed_forward("glu")
+class GatedMLP(FeedForward):
+    """down(act(gate(x)) * up(x)), no biases; ``activation``: "silu" or "gelu_tanh", computed in float32 on
+    the stacked product's float32 output.  Tensor names: ``gate_name``, ``up_name``, ``down_name`` (default
+    "gate", "up", "down").  The output is float32: it joins a float32 sum."""
+
+    ACTS = {"silu": 0, "gelu_tanh": 1}
+
+    def __init__(self, spec: PartSpec, rt=None):
+        super().__init__(spec, rt)
+        self.hidden = int(spec["hidden_size"])
+        self.inter = int(spec["intermediate_size"])
+        self.activation = spec.get("activation", "silu")
+        if self.activation not in self.ACTS:
+            raise ValueError(f"unknown activation {self.activation!r} of a gated feed-forward")
+        self.names = (spec.get("gate_name", "gate"), spec.get("up_name", "up"), spec.get("down_name", "down"))
+        self.gate_up = self.down = None
+        self.gate_block = self.inter
+
+    def kernel_modules(self):
+        return ("mixparts",)
+
+    def parameters(self):
+        g, u, d = self.names
+        return {g: ParamSpec((self.inter, self.hidden)), u: ParamSpec((self.inter, self.hidden)),
+                d: ParamSpec((self.hidden, self.inter))}
+
+    def load(self, tensors):
+        g, u, d = self.names
+        self.gate_up, self.gate_block = self.rt.glu_layout(tensors[g], tensors[u])
+        self.down = tensors[d].contiguous()
+
+    def forward(self, h, ctx: StepContext) -> Product:
+        rt, ws = ctx.rt, ctx.ws
+        act = rt.linear_glu(h, self.gate_up, self.gate_block, self.activation, ws, "ff_act")
+        return rt.linear(act, self.down, ws, "ff_out", out_dtype=torch.float32)

@@ -37,6 +37,8 @@ class RMSNorm(Norm):
         Returns the new rows in the compute dtype (x itself when that is float32): what the next
         product reads, since nothing normalises the stream again before it."""
         copy = None if ctx.rt.dtype == torch.float32 else ctx.ws.get(name, tuple(x.shape), ctx.rt.dtype)
+        if delta is not None:
+            delta = delta.settle_also(x)
         if delta is None:
             K.norm_mix(x, self.weight, self.eps, alpha=alpha, keep=keep, copy=copy)
         else:
@@ -47,9 +49,44 @@ class RMSNorm(Norm):
     def forward(self, x, ctx: StepContext, delta: Product | None = None, rows=None, name="h"):
         R = x.shape[0] if rows is None else rows.shape[0]
         out = ctx.ws.get(name, (R, self.width), ctx.rt.dtype)
+        if delta is not None:
+            delta = delta.settle_also(x)
         if delta is None:
             K.add_rmsnorm(x, self.weight, self.eps, out, rows=rows)
         else:
             K.add_rmsnorm(x, self.weight, self.eps, out, delta=delta.tensor, nsplit=delta.nsplit,
                           split_stride=delta.split_stride, rows=rows)
+        return out
+
+
+@register_norm("layernorm")
+class LayerNorm(Norm):
+    """y = (x - mean) / sqrt(var + eps) * weight with var the mean of the squared deviations, no bias,
+    in float32 from the float32 residual.  With ``delta`` the kernel adds it (and the product that
+    rides along as ``delta.also``: the two sublayers of a parallel block) to the residual first and
+    writes the sum back when all rows are processed."""
+
+    def __init__(self, spec: PartSpec, rt=None):
+        super().__init__(spec, rt)
+        self.width = int(spec["width"])
+        self.eps = float(spec["eps"])
+        self.weight_name = spec.get("weight_name", "weight")
+        self.weight = None
+
+    def kernel_modules(self):
+        return ("mixparts",)
+
+    def parameters(self):
+        return {self.weight_name: ParamSpec((self.width,), role="vector", init=("normal", 1.0, 0.1))}
+
+    def load(self, tensors):
+        self.weight = tensors[self.weight_name]
+
+    def forward(self, x, ctx: StepContext, delta: Product | None = None, rows=None, name="h"):
+        R = x.shape[0] if rows is None else rows.shape[0]
+        out = ctx.ws.get(name, (R, self.width), ctx.rt.dtype)
+        second = delta.also if delta is not None else None
+        if second is not None and second.also is not None:
+            second = second.settle_also(x)
+        K.add_layernorm(x, self.weight, self.eps, out, delta=delta, delta2=second, rows=rows)
         return out

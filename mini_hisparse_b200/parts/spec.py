@@ -113,10 +113,13 @@ class RunEntry:
 
     ``cache_of`` is None when the entry owns a cache of its own (it appends to it), or the
     index of an EARLIER entry of the run order whose cache this entry only reads.
+    ``before``: the key of a part of the model as a whole (ModelSpec.shared) that transforms the
+    residual stream right before this entry runs (the input of a pass over repeated layers).
     """
 
     layer: int
     cache_of: int | None = None
+    before: str | None = None
 
 
 @dataclass(frozen=True)
@@ -147,6 +150,8 @@ class ModelSpec:
                     raise ValueError(f"run entry {i} reads the cache of entry {e.cache_of}, which is not earlier")
                 if self.order[e.cache_of].cache_of is not None:
                     raise ValueError(f"run entry {i} reads entry {e.cache_of}, which owns no cache")
+            if e.before is not None and e.before not in {key for key, _, _ in self.shared}:
+                raise ValueError(f"run entry {i} runs the shared part {e.before!r} first, which the model lacks")
 
 
 def join_name(*pieces: str) -> str:
@@ -200,6 +205,18 @@ class PagedKVNeed(PagedNeed):
         if self.v_dim is None:
             return (2, self.kv_heads, page_size, self.head_dim)
         return (self.kv_heads * page_size * (self.head_dim + self.v_dim),)
+
+
+@dataclass(frozen=True)
+class PagedRowsNeed(PagedNeed):
+    """One row of ``width`` numbers per cached position and nothing else: a page is [page_size, width].
+    What the row means is its mixer's business (a latent that is key and value at once, say)."""
+
+    width: int = 16
+    window: int | None = None
+
+    def page_shape(self, page_size: int) -> tuple[int, ...]:
+        return (page_size, self.width)
 
 
 @dataclass(frozen=True)
