@@ -17,9 +17,9 @@ of 128 to 4,096 tokens in portions of 512 beside decoding at the Qwen2.5-14B sha
 8,192 prompt tokens plus 512 generated ones at the Qwen2.5-32B shape with the page pool sized from
 free memory; tokens a second, step-time percentiles, roofline fractions, clocks, and the layer count.
 
-    python bench.py --workload koronex [--sizes 2k,4k]
+    python bench.py --workload koronex|dotivik [--sizes 2k,4k]
 
-times the Koronex design beside the Qwen2 dense model at equal width, heads, feed-forward width and layer
+times the Koronex or the Dotivik design beside the Qwen2 dense model at equal width, heads, feed-forward width and layer
 count (random weights): prefill of a 2,048-token prompt and decode at batch 8 with 4,096 tokens of context,
 each with its kernels' times, as one JSON line.
 """
@@ -68,10 +68,12 @@ def workload(args) -> int:
 def compare(args) -> int:
     from mini_hisparse_b200 import measure
 
-    result = measure.compare_architectures(tuple(args.sizes.split(",")), steps=args.steps, warmup=args.warmup)
+    design = args.workload
+    result = measure.compare_architectures(tuple(args.sizes.split(",")), design=design, steps=args.steps,
+                                           warmup=args.warmup)
     first = result["sizes"][args.sizes.split(",")[0]]
-    line = {"metric": "Koronex beside Qwen2 at equal size: prefill and decode tokens/s", "unit": "tokens/s",
-            "value": first["koronex"]["decode"]["tokens_per_s"], "n_gpus": 1, "higher_is_better": True,
+    line = {"metric": f"{design.capitalize()} beside Qwen2 at equal size: prefill and decode tokens/s", "unit": "tokens/s",
+            "value": first[design]["decode"]["tokens_per_s"], "n_gpus": 1, "higher_is_better": True,
             "impl": "ours", "dtype": "bf16", "data": "synthetic: seeded random weights and token ids", **result}
     print(json.dumps(line))
     return 0
@@ -88,9 +90,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the 28 of the config")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["koronex"],
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["koronex", "dotivik"],
                     help="run a serving workload, or the two-architecture comparison, instead of the decode bench")
-    ap.add_argument("--sizes", default="2k,4k", help="with --workload koronex: which sizes to time")
+    ap.add_argument("--sizes", default="2k,4k", help="with --workload koronex or dotivik: which sizes to time")
     ap.add_argument("--graph-after", type=int, default=8,
                     help="with --workload: capture a decode graph at the N-th step that asks for it")
     args = ap.parse_args()
@@ -102,7 +104,7 @@ def main() -> int:
     if args.impl == "reference":
         return reference_arm(args)
     args.warmup = max(args.warmup, 3)
-    if args.workload == "koronex":
+    if args.workload in ("koronex", "dotivik"):
         if args.steps == 64:
             args.steps = 32
         return compare(args)

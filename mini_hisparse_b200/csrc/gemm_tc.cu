@@ -154,7 +154,17 @@ template <typename OT> __device__ __forceinline__ void store_out(OT* p, float v)
 template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
 template <> __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 
-__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + expf(-g)) * u; }
+// EPI 1 and 3 are the gated epilogues: act(gate) * up with act = silu (1) or the tanh form of gelu (3).
+__host__ __device__ constexpr bool is_glu(int epi) { return epi == 1 || epi == 3; }
+template <int EPI>
+__device__ __forceinline__ float glu_mul(float g, float u) {
+    if constexpr (EPI == 3) {
+        const float c = 0.7978845608028654f;      // sqrt(2 / pi)
+        return 0.5f * g * (1.f + tanhf(c * (g + 0.044715f * g * g * g))) * u;
+    } else {
+        return g / (1.f + expf(-g)) * u;
+    }
+}
 
 // C element of (a-row ra, b-row rb): TRANSPOSED ? C[rb, ra] : C[ra, rb].
 // EPI = 1 (SwiGLU): the weight operand holds gate and up rows interleaved in blocks of 16
@@ -269,8 +279,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         else pdl_wait();       // nothing was loaded: still do not write before the previous kernel is done
         tc_fence_after();
         OT* Cz = C + (size_t)blockIdx.z * split_stride;
-        if (ok && EPI == 1) {
-            if constexpr (EPI == 1 && TRANSPOSED) {
+        if (ok && is_glu(EPI)) {
+            if constexpr (is_glu(EPI) && TRANSPOSED) {
                 // lanes 0-15 of a warp hold gate rows, lanes 16-31 the up rows of the same block
                 const int out_col = (ra0 + quarter * 32) / 2 + (lane & 15);
 #pragma unroll 1
@@ -284,10 +294,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         const float up = __shfl_down_sync(0xffffffffu, mine, 16);
                         const int rb = rb0 + c0 + j;
                         if (lane < 16 && rb < Rb && 2 * out_col < Ra)
-                            store_out<OT>(C + (size_t)rb * ldc + out_col, silu_mul(mine, up));
+                            store_out<OT>(C + (size_t)rb * ldc + out_col, glu_mul<EPI>(mine, up));
                     }
                 }
-            } else if constexpr (EPI == 1) {
+            } else if constexpr (is_glu(EPI)) {
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN; c0 += 32) {
                     uint32_t g[16], u[16];     // the loads are warp-wide: every lane takes part
@@ -299,7 +309,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     OT* row = C + (size_t)ra * ldc + oc;
                     float v[16];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) v[j] = silu_mul(__uint_as_float(g[j]), __uint_as_float(u[j]));
+                    for (int j = 0; j < 16; ++j) v[j] = glu_mul<EPI>(__uint_as_float(g[j]), __uint_as_float(u[j]));
                     if (rb0 + c0 + 32 <= Rb && ((uintptr_t)row & 15) == 0 && sizeof(OT) == 2) {
                         uint32_t p[8];
 #pragma unroll
@@ -423,11 +433,11 @@ template <typename OT, int EPI>
 __device__ __forceinline__ void emit_unit(OT* __restrict__ C, long long ldc, int Ra, int Rb, int ra, int rb0, int c0,
                                           const uint32_t (&r)[16], const uint32_t (&r2)[16]) {
     if (ra >= Ra) return;
-    if constexpr (EPI == 1) {
+    if constexpr (is_glu(EPI)) {
         OT* row = C + (size_t)ra * ldc + (rb0 + c0) / 2;
         float v[16];
 #pragma unroll
-        for (int x = 0; x < 16; ++x) v[x] = silu_mul(__uint_as_float(r[x]), __uint_as_float(r2[x]));
+        for (int x = 0; x < 16; ++x) v[x] = glu_mul<EPI>(__uint_as_float(r[x]), __uint_as_float(r2[x]));
         if (rb0 + c0 + 32 <= Rb && ((uintptr_t)row & 15) == 0 && sizeof(OT) == 2) {
             uint32_t p[8];
 #pragma unroll
@@ -474,7 +484,7 @@ template <typename OT, int EPI>
 __device__ __forceinline__ void store_tile(uint32_t acc, int ra0, int rb0, int bn, int row_in_tile, OT* __restrict__ C,
                                            long long ldc, int Ra, int Rb, const QkvRopeArgs& qr,
                                            int* __restrict__ status) {
-    constexpr int UNIT = EPI == 1 ? 32 : 16;        // columns that are stored together
+    constexpr int UNIT = is_glu(EPI) ? 32 : 16;        // columns that are stored together
     if constexpr (EPI == 2) {
         const int ra = ra0 + row_in_tile;
         const bool live = ra < Ra;
@@ -639,7 +649,7 @@ __device__ __forceinline__ void store_tile(uint32_t acc, int ra0, int rb0, int b
         for (int c0 = 0; c0 < bn; c0 += UNIT) {
             uint32_t r[16], r2[16];
             tmem_ld16(acc + c0, r);
-            if constexpr (EPI == 1) tmem_ld16(acc + c0 + 16, r2);
+            if constexpr (is_glu(EPI)) tmem_ld16(acc + c0 + 16, r2);
             tmem_ld_wait();
             emit_unit<OT, EPI>(C, ldc, Ra, Rb, ra0 + row_in_tile, rb0, c0, r, r2);
         }
@@ -787,7 +797,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     } else {
         const int quarter = warp & 3;
         const int row_in_tile = quarter * 32 + lane;
-        constexpr int UNIT = EPI == 1 ? 32 : 16;        // columns that are stored together
+        constexpr int UNIT = is_glu(EPI) ? 32 : 16;        // columns that are stored together
         // ---- second pass: the shared tiles.  The CTAs that hold parts of a tile divide its columns
         // among themselves; each adds the parts in the order of their K ranges and stores. ---------
         auto reduce_shared = [&](const int (&shared_entry)[2], int shared_count) {
@@ -806,9 +816,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 #pragma unroll
                 for (int x = 0; x < 16; ++x) s[x] = s2[x] = 0.f;
                 // the loads of several parts are in flight together; the sums stay in the parts' order
-                constexpr int BATCH = EPI == 1 ? 2 : 4;
+                constexpr int BATCH = is_glu(EPI) ? 2 : 4;
                 for (int p0 = 0; p0 < parts; p0 += BATCH) {
-                    uint4 v[BATCH][4], w[EPI == 1 ? BATCH : 1][4];
+                    uint4 v[BATCH][4], w[is_glu(EPI) ? BATCH : 1][4];
 #pragma unroll
                     for (int q = 0; q < BATCH; ++q) {
                         const int p = p0 + q < parts ? p0 + q : parts - 1;
@@ -817,7 +827,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                         const uint4* a = (const uint4*)(src + ((size_t)(c0 >> 4) * BM + row_in_tile) * 16);
 #pragma unroll
                         for (int x = 0; x < 4; ++x) v[q][x] = __ldcg(a + x);
-                        if constexpr (EPI == 1) {
+                        if constexpr (is_glu(EPI)) {
 #pragma unroll
                             for (int x = 0; x < 4; ++x) w[q][x] = __ldcg(a + BM * 4 + x);    // the next 16 columns: the up half
                         }
@@ -830,7 +840,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                                 s[4 * x] += __uint_as_float(v[q][x].x); s[4 * x + 1] += __uint_as_float(v[q][x].y);
                                 s[4 * x + 2] += __uint_as_float(v[q][x].z); s[4 * x + 3] += __uint_as_float(v[q][x].w);
                             }
-                            if constexpr (EPI == 1) {
+                            if constexpr (is_glu(EPI)) {
 #pragma unroll
                                 for (int x = 0; x < 4; ++x) {
                                     s2[4 * x] += __uint_as_float(w[q][x].x); s2[4 * x + 1] += __uint_as_float(w[q][x].y);
@@ -1219,7 +1229,7 @@ int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, void* C, i
         // the narrow tiles stream weights: two CTAs per SM (<= 112 KB each) overlap one CTA's
         // start-up and epilogue with the other's loads
         case 16:
-            if (EPI == 1 && !TRANSPOSED) break;      // the SwiGLU epilogue pairs 16 + 16 columns
+            if (is_glu(EPI) && !TRANSPOSED) break;      // the SwiGLU epilogue pairs 16 + 16 columns
             return launch<16, 6, TRANSPOSED, OT, EPI>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, co, status, st);
         case 32: return launch<32, 5, TRANSPOSED, OT, EPI>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, co, status, st);
         case 64: return launch<64, 4, TRANSPOSED, OT, EPI>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, co, status, st);
@@ -1281,7 +1291,7 @@ int launch_persistent(const void* X, const void* W, void* C, int M, int N, int K
         if (sms <= 0) sms = 148;
         if (sms > P_MAX_CTAS) sms = P_MAX_CTAS;
     }
-    const int step = EPI == 1 ? 32 : 16;
+    const int step = is_glu(EPI) ? 32 : 16;
     int bn = N >= P_BN_MAX ? P_BN_MAX : (N + step - 1) / step * step;
     const int tiles_m = (M + BM - 1) / BM;
     long long num_tiles = (long long)tiles_m * ((N + bn - 1) / bn);
@@ -1313,7 +1323,7 @@ int launch_persistent(const void* X, const void* W, void* C, int M, int N, int K
         const int pairs = sms / 2;
         int pbn = N >= P_BN_MAX ? P_BN_MAX : (N + 31) / 32 * 32;
         const int tiles_m2 = (M + 2 * BM - 1) / (2 * BM);
-        if (EPI != 2 && N >= P_BN_MAX) pbn = choose_persistent_bn(tiles_m2, N, pairs, EPI == 1 ? 32 : 16);
+        if (EPI != 2 && N >= P_BN_MAX) pbn = choose_persistent_bn(tiles_m2, N, pairs, is_glu(EPI) ? 32 : 16);
         if (EPI == 2 && qr && qr->d <= 128 && N >= P_BN_MAX) {
             // tiles begin and end on heads: 256 wide, or 128 where that fills the rounds of pairs better
             const long long wide = ((long long)tiles_m2 * ((N + 255) / 256) + pairs - 1) / pairs * (256 + 24);
@@ -1464,9 +1474,10 @@ MHB_EXPORT int mhb_gemm_tc_qkv_rope(const void* X, const void* W, int M, int K, 
 
 // act[M, I] = silu(X Wg^T) * (X Wu^T) where W [2 I, K] holds gate and up rows interleaved in
 // blocks of 16 (see the kernel).  I must be a multiple of 16; no split K.
-MHB_EXPORT int mhb_gemm_tc_swiglu(const void* X, const void* W, void* C, int c_dtype, int M, int I, int K,
-                                  long long lda, long long ldw, long long ldc, int swap, int bn, float* partials,
-                                  int* flags, int* status, cudaStream_t stream) {
+template <int EPI>
+static int gemm_tc_glu(const void* X, const void* W, void* C, int c_dtype, int M, int I, int K,
+                       long long lda, long long ldw, long long ldc, int swap, int bn, float* partials,
+                       int* flags, int* status, cudaStream_t stream) {
     if (M <= 0 || I <= 0) return 0;
     if (I % 16) return fail("gemm_tc_swiglu: the intermediate size %d must be a multiple of 16", I);
     if (K <= 0 || K % 8 || lda % 8 || ldw % 8) return fail("gemm_tc: K, lda and ldw must be multiples of 8 (K %d, lda %lld, ldw %lld)", K, lda, ldw);
@@ -1479,11 +1490,26 @@ MHB_EXPORT int mhb_gemm_tc_swiglu(const void* X, const void* W, void* C, int c_d
     if (swap) {
         if ((rc = make_map(&ma, W, N, K, ldw, BM))) return rc;
         if ((rc = make_map(&mb, X, M, K, lda, bn))) return rc;
-        return dispatch_bn<true, __nv_bfloat16, 1>(bn, ma, mb, C, N, M, K, ldc, 1, total_kb, 0, 1, status, stream);
+        return dispatch_bn<true, __nv_bfloat16, EPI>(bn, ma, mb, C, N, M, K, ldc, 1, total_kb, 0, 1, status, stream);
     }
     if (bn == 0)
-        return launch_persistent<__nv_bfloat16, 1>(X, W, C, M, N, K, lda, ldw, ldc, partials, flags, status, stream);
+        return launch_persistent<__nv_bfloat16, EPI>(X, W, C, M, N, K, lda, ldw, ldc, partials, flags, status, stream);
     if ((rc = make_map(&ma, X, M, K, lda, BM))) return rc;
     if ((rc = make_map(&mb, W, N, K, ldw, bn))) return rc;
-    return dispatch_bn<false, __nv_bfloat16, 1>(bn, ma, mb, C, M, N, K, ldc, 1, total_kb, 0, 2, status, stream);
+    return dispatch_bn<false, __nv_bfloat16, EPI>(bn, ma, mb, C, M, N, K, ldc, 1, total_kb, 0, 2, status, stream);
+}
+
+MHB_EXPORT int mhb_gemm_tc_swiglu(const void* X, const void* W, void* C, int c_dtype, int M, int I, int K,
+                                  long long lda, long long ldw, long long ldc, int swap, int bn, float* partials,
+                                  int* flags, int* status, cudaStream_t stream) {
+    return gemm_tc_glu<1>(X, W, C, c_dtype, M, I, K, lda, ldw, ldc, swap, bn, partials, flags, status, stream);
+}
+
+// The same with the activation as a parameter: act 0 = silu, 1 = the tanh form of gelu.
+MHB_EXPORT int mhb_gemm_tc_glu(const void* X, const void* W, void* C, int c_dtype, int M, int I, int K,
+                               long long lda, long long ldw, long long ldc, int swap, int bn, float* partials,
+                               int* flags, int* status, int act, cudaStream_t stream) {
+    if (act == 0) return gemm_tc_glu<1>(X, W, C, c_dtype, M, I, K, lda, ldw, ldc, swap, bn, partials, flags, status, stream);
+    if (act == 1) return gemm_tc_glu<3>(X, W, C, c_dtype, M, I, K, lda, ldw, ldc, swap, bn, partials, flags, status, stream);
+    return fail("gemm_tc_glu: unknown activation %d", act);
 }

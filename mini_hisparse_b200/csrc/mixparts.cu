@@ -12,6 +12,7 @@
 //   head_linear        out[t, h, :] = W[h] x[t, h, :]: one small matrix per head
 //   maps_combine       o = a1 - lambda a2, o / rms(o) * post, times sigmoid(gate_h)
 #include "common.cuh"
+#include "mma_helpers.cuh"
 
 using namespace mhb;
 
@@ -37,12 +38,12 @@ __device__ __forceinline__ float siluf(float z) { return z / (1.f + expf(-z)); }
 // For output row r (source row s = rows ? rows[r] : r): v = x[s] + d1[s] + d2[s]; without `rows` the sum
 // is written back (the residual is updated in place).  mean and variance (the mean of the squared
 // deviations, taken in a second pass over the row) in float32.
-template <typename DT, typename OT>
+template <typename DT, typename OT, bool VEC>
 __global__ void add_layernorm_kernel(float* __restrict__ x, const DT* __restrict__ d1, int n1, size_t s1,
                                      const DT* __restrict__ d2, int n2, size_t s2,
                                      const float* __restrict__ weight, float eps, const int* __restrict__ rows,
                                      OT* __restrict__ out, int H) {
-    extern __shared__ float row[];
+    extern __shared__ __align__(16) float row[];
     __shared__ float scratch[33];
     pdl_launch_dependents();
     pdl_wait();
@@ -51,13 +52,32 @@ __global__ void add_layernorm_kernel(float* __restrict__ x, const DT* __restrict
     float* xr = x + (size_t)s * H;
     const bool write_back = (d1 != nullptr || d2 != nullptr) && rows == nullptr;
     float sum = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float v = xr[i];
-        if (d1) v += load_parts(d1, (size_t)s * H + i, n1, s1);
-        if (d2) v += load_parts(d2, (size_t)s * H + i, n2, s2);
-        if (write_back) xr[i] = v;
-        row[i] = v;
-        sum += v;
+    if (VEC) {          // four elements per thread and load (rows and parts 16-byte aligned, float32 products)
+        const float* f1 = (const float*)d1;
+        const float* f2 = (const float*)d2;
+        for (int i = 4 * threadIdx.x; i < H; i += 4 * blockDim.x) {
+            float4 v = *(const float4*)(xr + i);
+            if (f1) for (int p = 0; p < n1; ++p) {
+                const float4 a = *(const float4*)(f1 + (size_t)p * s1 + (size_t)s * H + i);
+                v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+            }
+            if (f2) for (int p = 0; p < n2; ++p) {
+                const float4 a = *(const float4*)(f2 + (size_t)p * s2 + (size_t)s * H + i);
+                v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+            }
+            if (write_back) *(float4*)(xr + i) = v;
+            *(float4*)(row + i) = v;
+            sum += (v.x + v.y) + (v.z + v.w);
+        }
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            float v = xr[i];
+            if (d1) v += load_parts(d1, (size_t)s * H + i, n1, s1);
+            if (d2) v += load_parts(d2, (size_t)s * H + i, n2, s2);
+            if (write_back) xr[i] = v;
+            row[i] = v;
+            sum += v;
+        }
     }
     const float mean = block_sum(sum, scratch) / (float)H;
     float sq = 0.f;
@@ -311,6 +331,70 @@ head_linear_kernel(const XT* __restrict__ x, size_t xs_t, size_t xs_h, const WT*
     }
 }
 
+// The same on the tensor cores (bfloat16 in, float32 accumulation): one CTA per 64 tokens x 64 outputs of a
+// head; both tiles are staged whole by cp.async (K padded to a multiple of 32 with zeros), each warp owns 16
+// tokens and walks K with mma.sync m16n8k16.  x's strides and K must be multiples of 8 elements.
+constexpr int HM_T = 64, HM_N = 64;
+template <typename OT>
+__global__ void __launch_bounds__(128)
+head_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, size_t xs_t, size_t xs_h, const __nv_bfloat16* __restrict__ w,
+                       OT* __restrict__ out, size_t os_t, size_t os_h, int T, int N, int K, int KP) {
+    extern __shared__ __align__(16) uint8_t hm_smem[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int LD = KP + 8;                      // padded row, in elements: keeps ldmatrix free of bank conflicts
+    const uint32_t xs = (uint32_t)__cvta_generic_to_shared(hm_smem);
+    const uint32_t ws = xs + HM_T * LD * 2;
+    const int t0 = blockIdx.x * HM_T, n0 = blockIdx.y * HM_N, h = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const __nv_bfloat16* wh = w + (size_t)h * N * K;
+    const int cpr = KP / 8;                     // 16-byte chunks per row
+    for (int c = tid; c < HM_T * cpr; c += 128) {
+        const int r = c / cpr, ch = c - r * cpr;
+        const bool live = t0 + r < T && ch * 8 < K;
+        const __nv_bfloat16* src = live ? x + (size_t)(t0 + r) * xs_t + (size_t)h * xs_h + ch * 8 : x;
+        cp_async16(xs + (r * LD + ch * 8) * 2, src, live ? 16 : 0);
+    }
+    for (int c = tid; c < HM_N * cpr; c += 128) {
+        const int r = c / cpr, ch = c - r * cpr;
+        const bool live = n0 + r < N && ch * 8 < K;
+        const __nv_bfloat16* src = live ? wh + (size_t)(n0 + r) * K + ch * 8 : wh;
+        cp_async16(ws + (r * LD + ch * 8) * 2, src, live ? 16 : 0);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+    float acc[HM_N / 8][4];
+#pragma unroll
+    for (int j = 0; j < HM_N / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    const int wrow = warp * 16;
+    for (int k = 0; k < KP; k += 32) {
+        uint32_t a0[4], a1[4];
+        const int r = wrow + (lane & 7) + 8 * ((lane >> 3) & 1), c = k + 8 * (lane >> 4);
+        ldmatrix_x4(xs + (r * LD + c) * 2, a0[0], a0[1], a0[2], a0[3]);
+        ldmatrix_x4(xs + (r * LD + c + 16) * 2, a1[0], a1[1], a1[2], a1[3]);
+#pragma unroll
+        for (int j = 0; j < HM_N / 8; ++j) {
+            uint32_t b0, b1, b2, b3;          // 8 outputs x 32 elements of K
+            ldmatrix_x4(ws + ((j * 8 + (lane & 7)) * LD + k + 8 * (lane >> 3)) * 2, b0, b1, b2, b3);
+            mma_bf16(acc[j], a0, b0, b1);
+            mma_bf16(acc[j], a1, b2, b3);
+        }
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int t = t0 + wrow + (lane >> 2) + 8 * half;
+        if (t >= T) continue;
+        OT* o = out + (size_t)t * os_t + (size_t)h * os_h;
+#pragma unroll
+        for (int j = 0; j < HM_N / 8; ++j) {
+            const int n = n0 + j * 8 + (lane & 3) * 2;
+            if (n < N) o[n] = from_float<OT>(acc[j][2 * half]);
+            if (n + 1 < N) o[n + 1] = from_float<OT>(acc[j][2 * half + 1]);
+        }
+    }
+}
+
 // ---- the maps of a head into one output ------------------------------------------------------------------
 // a [T, heads, 2, dv] float32 (map 1, map 2 of every head); o = a1 - lambda * a2; o <- o / sqrt(mean(o^2) + eps)
 // * post; times sigmoid(gate[t][h]) if there is a gate (one column per head of a float32 product).
@@ -358,13 +442,28 @@ MHB_EXPORT int mhb_add_layernorm(float* x, const void* d1, int n1, long long s1,
     if (R <= 0) return 0;
     if ((n1 > 1 || n2 > 1) && delta_dtype != MHB_F32) return fail("add_layernorm: split partials must be float32");
     const size_t smem = sizeof(float) * (size_t)H;
+    const bool vec = delta_dtype == MHB_F32 && H % 4 == 0 && s1 % 4 == 0 && s2 % 4 == 0 && ((uintptr_t)x & 15) == 0 &&
+                     ((uintptr_t)d1 & 15) == 0 && ((uintptr_t)d2 & 15) == 0;
+    const int threads = vec ? row_threads(H / 4) : row_threads(H);
+    if (vec) {
+        MHB_DISPATCH_DTYPE(out_dtype, OT, {
+            auto kern = add_layernorm_kernel<float, OT, true>;
+            if (smem > 48 * 1024) {
+                cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                if (e != cudaSuccess) return fail("add_layernorm: a row of %d: %s", H, cudaGetErrorString(e));
+            }
+            launch_kernel(kern, dim3(R), dim3(threads), smem, stream, x, (const float*)d1, n1, (size_t)s1,
+                          (const float*)d2, n2, (size_t)s2, weight, eps, rows, (OT*)out, H);
+        });
+        return check_launch("add_layernorm");
+    }
     MHB_DISPATCH_DTYPE(delta_dtype, DT, MHB_DISPATCH_DTYPE(out_dtype, OT, {
-        auto kern = add_layernorm_kernel<DT, OT>;
+        auto kern = add_layernorm_kernel<DT, OT, false>;
         if (smem > 48 * 1024) {
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return fail("add_layernorm: a row of %d: %s", H, cudaGetErrorString(e));
         }
-        launch_kernel(kern, dim3(R), dim3(row_threads(H)), smem, stream, x, (const DT*)d1, n1, (size_t)s1,
+        launch_kernel(kern, dim3(R), dim3(threads), smem, stream, x, (const DT*)d1, n1, (size_t)s1,
                       (const DT*)d2, n2, (size_t)s2, weight, eps, rows, (OT*)out, H);
     }));
     return check_launch("add_layernorm");
@@ -439,6 +538,22 @@ MHB_EXPORT int mhb_head_linear(const void* x, int x_dtype, long long xs_t, long 
                                cudaStream_t stream) {
     if (T <= 0 || heads <= 0 || N <= 0) return 0;
     if (heads > 65535) return fail("head_linear: too many heads");
+    const int KP = (K + 31) / 32 * 32;
+    const size_t smem = (size_t)(HM_T + HM_N) * (KP + 8) * 2;
+    if (x_dtype == MHB_BF16 && w_dtype == MHB_BF16 && K % 8 == 0 && xs_t % 8 == 0 && xs_h % 8 == 0 &&
+        ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0 && smem <= 200 * 1024) {
+        dim3 grid((T + HM_T - 1) / HM_T, (N + HM_N - 1) / HM_N, heads);
+        MHB_DISPATCH_DTYPE(out_dtype, OT, {
+            auto kern = head_linear_mma_kernel<OT>;
+            if (smem > 48 * 1024) {
+                cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                if (e != cudaSuccess) return fail("head_linear: shared memory %zu: %s", smem, cudaGetErrorString(e));
+            }
+            launch_kernel(kern, grid, dim3(128), smem, stream, (const __nv_bfloat16*)x, (size_t)xs_t, (size_t)xs_h,
+                          (const __nv_bfloat16*)w, (OT*)out, (size_t)os_t, (size_t)os_h, T, N, K, KP);
+        });
+        return check_launch("head_linear");
+    }
     dim3 grid((T + HL_T - 1) / HL_T, (N + HL_N - 1) / HL_N, heads);
     MHB_DISPATCH_DTYPE(x_dtype, XT, MHB_DISPATCH_DTYPE(w_dtype, WT, MHB_DISPATCH_DTYPE(out_dtype, OT,
         launch_kernel(head_linear_kernel<XT, WT, OT>, grid, dim3(128), 0, stream, (const XT*)x, (size_t)xs_t,

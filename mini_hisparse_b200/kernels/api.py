@@ -116,6 +116,7 @@ def norm_mix(x, weight, eps, *, delta=None, nsplit=1, split_stride=0, alpha=1.0,
 
 
 ACTIVATIONS = {"relu2": 0, "silu": 1, "gelu_tanh": 2, "copy": 3}
+GLU_ACTS = {"silu": 0, "gelu_tanh": 1}          # activations of a gated feed-forward's gate
 
 
 def act_rows(z, out, act: str, nsplit=1, split_stride=0):
@@ -386,6 +387,25 @@ def gemm_tc_swiglu(a, w, out, *, swap: bool, bn: int, status=None, scratch=None)
         _ptr(a), _ptr(w), _ptr(out), c_int(dtype_code(out.dtype)), c_int(M), c_int(I), c_int(K),
         c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
         c_int(1 if swap else 0), c_int(bn), *_scratch_ptrs(scratch), _ptr(status), _stream()), "gemm_tc_swiglu")
+
+
+def gemm_tc_glu(a, w, out, act: str, *, swap: bool, bn: int, status=None, scratch=None):
+    """gemm_tc_swiglu with the gate's activation as a parameter: "silu" or "gelu_tanh" (taken in float32 on the
+    accumulators, in the product's epilogue)."""
+    lib = build.load("gemm_tc")
+    M, K = a.shape
+    I = out.shape[1]
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("gemm_tc_glu: operands and output must be bfloat16")
+    if w.shape != (2 * I, K):
+        raise KernelError(f"gemm_tc_glu: w is {list(w.shape)}, expected [{2 * I}, {K}]")
+    if swap and M > bn:
+        raise KernelError(f"gemm_tc: {M} tokens do not fit the swapped tile of {bn}")
+    _check(lib, lib.mhb_gemm_tc_glu(
+        _ptr(a), _ptr(w), _ptr(out), c_int(dtype_code(out.dtype)), c_int(M), c_int(I), c_int(K),
+        c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
+        c_int(1 if swap else 0), c_int(bn), *_scratch_ptrs(scratch), _ptr(status), c_int(GLU_ACTS[act]), _stream()),
+        "gemm_tc_glu")
 
 
 def rope_table(positions, inv_freq, table):
@@ -761,9 +781,6 @@ def stream_pack(x, dst, col0: int, delta=None, delta2=None, zero: bool = False):
     _check(lib, lib.mhb_stream_pack(_ptr(x), a[0], a[1], a[2], b[0], b[1], b[2], c_int(_delta_dtype(delta, delta2)),
                                     _ptr(dst), c_int(dtype_code(dst.dtype)), c_int(dst.stride(0)), c_int(col0),
                                     c_int(T), c_int(W), c_int(1 if zero else 0), _stream()), "stream_pack")
-
-
-GLU_ACTS = {"silu": 0, "gelu_tanh": 1}
 
 
 def glu_act(gate_up, out, act: str, nsplit=1, split_stride=0, block=None):

@@ -75,6 +75,26 @@ class BFloat16Runtime(Runtime):
         K.swiglu(gu.tensor, out, nsplit=gu.nsplit, split_stride=gu.split_stride, block=block)
         return out
 
+    def glu_layout(self, gate: torch.Tensor, up: torch.Tensor):
+        return self.swiglu_layout(gate, up)
+
+    def linear_glu(self, x, weight, block: int, activation: str, ws: Workspace, name: str) -> torch.Tensor:
+        """act(x Wg^T) * (x Wu^T) for a weight from glu_layout(): the activation ("silu", "gelu_tanh") is fused
+        into the product's epilogue when the layout is interleaved, else the product is followed by the
+        activation kernel."""
+        M, Kd = x.shape
+        I = weight.shape[0] // 2
+        if (block == self.GATE_BLOCK and x.dtype == torch.bfloat16 and x.stride(0) % 8 == 0 and Kd % 8 == 0
+                and x.data_ptr() % 16 == 0):
+            out = ws.get(name, (M, I), self.dtype)
+            if M <= 64:
+                K.gemm_tc_glu(x, weight, out, activation, swap=True, bn=(16 if M <= 16 else 32 if M <= 32 else 64),
+                              status=self.status)
+            else:
+                K.gemm_tc_glu(x, weight, out, activation, swap=False, bn=0, status=self.status, scratch=self.scratch())
+            return out
+        return super().linear_glu(x, weight, block, activation, ws, name)
+
     def qkv_rope_append(self, x, weight, bias, ctx, position, block_table, q_out, cache_storage, *,
                         nq, nkv, d, page_size, write_kv) -> bool:
         """More than 64 tokens and head size 64 or 128: the persistent product's epilogue rotates and

@@ -405,6 +405,26 @@ def koronex_shape(width: int, heads: int, kv_heads: int, head_dim: int, ff: int,
                 postln_alpha=1.0, token_side=dict(dim=side_dim), layers=out)
 
 
+def dotivik_shape(width: int, heads: int, kv_heads: int, head_dim: int, ff: int, layers: int, vocab: int,
+                  window: int = 1024, kv_rank: int = 96, rot_dim: int = 32) -> dict:
+    """A Dotivik config.json of a real model's sizes with ``layers`` layer RUNS: groups of three layers (latent
+    attention, attention with two score maps per head, latent attention), of which the middle of the model
+    runs twice, every layer with a feed-forward.  Latent layers have ``heads`` heads (head_dim unrotated and
+    rot_dim rotated elements, values head_dim wide) over a cache row of kv_rank + rot_dim = 128 numbers; map
+    layers have heads / 2 heads with two maps of head_dim / 2 each and values head_dim wide."""
+    lat = dict(heads=heads, dim=head_dim, rot_dim=rot_dim, vdim=head_dim, kv_rank=kv_rank,
+               scale=(head_dim + rot_dim) ** -0.5, mask=dict(size=window), rot=dict(dims=rot_dim, base=10000.0))
+    att = dict(heads=heads // 2, kv_heads=max(1, kv_heads // 2), dim=head_dim // 2, vdim=head_dim,
+               scale=(head_dim // 2) ** -0.5, softcap=50.0, diff=0.5, rot=dict(dims=head_dim // 2, base=10000.0))
+    repeat = max(1, layers // 4)                       # layers of the run that goes twice
+    stored = layers - repeat
+    out = [dict(type="attention" if i % 3 == 1 else "latent_attention", mixer=dict(att if i % 3 == 1 else lat),
+                mlp=dict(kind="dense", ff=ff)) for i in range(stored)]
+    start = (stored - repeat) // 2
+    return dict(architecture="Dotivik", vocab=vocab, width=width, norm=dict(eps=1e-5), layers=out,
+                loop=dict(start=start, stop=start + repeat, times=2))
+
+
 def qwen2_shape(width: int, heads: int, kv_heads: int, head_dim: int, ff: int, layers: int, vocab: int) -> dict:
     return dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", vocab_size=vocab, hidden_size=width,
                 intermediate_size=ff, num_hidden_layers=layers, num_attention_heads=heads,
@@ -540,6 +560,14 @@ def architecture_point(config: dict, *, prefill_tokens=2048, batch=8, context=40
     state = sum(2 * grp.storage[:, :batch].numel() * grp.storage.element_size() for grp in cache.state_groups)
     emb = model.embedding.weight
     nbytes = model.weight_bytes() - emb.numel() * emb.element_size() + kv + state
+    if getattr(model.head, "tied", False):
+        nbytes += emb.numel() * emb.element_size()            # the table is the head's weight: read whole
+    runs: dict[int, int] = {}
+    for e in model.spec.order:                                 # a layer that runs again reads its weights again
+        runs[e.layer] = runs.get(e.layer, 0) + 1
+    for i, n in runs.items():
+        if n > 1:
+            nbytes += (n - 1) * sum(p.nbytes() for p in model.blocks[i].parts().values())
     p = peaks()
     out["decode"] = {"batch": batch, "context": context, "ms_per_step": ms, "tokens_per_s": batch / (ms / 1e3),
                      "bytes": nbytes, "gbs": nbytes / (ms / 1e3) / 1e9, "hbm_frac": nbytes / (ms / 1e3) / 1e9 / p["hbm_gbs"],
@@ -563,14 +591,18 @@ COMPARE_SIZES = {
 }
 
 
-def compare_architectures(sizes=("2k", "4k"), **kw) -> dict:
-    """Koronex beside the Qwen2 dense model at equal width, heads, feed-forward width and layer count."""
+DESIGN_SHAPES = {"koronex": koronex_shape, "dotivik": dotivik_shape}
+
+
+def compare_architectures(sizes=("2k", "4k"), design: str = "koronex", **kw) -> dict:
+    """``design`` (Koronex or Dotivik) beside the Qwen2 dense model at equal width, heads, feed-forward width
+    and count of layer runs."""
     out = {"peaks": peaks(), "sizes": {}}
     for name in sizes:
         shape = COMPARE_SIZES[name]
         out["sizes"][name] = {
             "shape": dict(zip(("width", "heads", "kv_heads", "head_dim", "ff", "layers", "vocab"), shape)),
-            "koronex": architecture_point(koronex_shape(*shape), **kw),
+            design: architecture_point(DESIGN_SHAPES[design](*shape), **kw),
             "qwen2": architecture_point(qwen2_shape(*shape), **kw),
         }
     return out

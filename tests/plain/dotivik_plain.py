@@ -129,16 +129,17 @@ def differential_attention(cfg, w, p, m, h, positions):
     k = rotate_interleaved(k.reshape(T, 2 * G, d), positions, r, base).view(T, G, 2, d)
     lam = (torch.exp((w[p + "lq1"] * w[p + "lk1"]).sum()) - torch.exp((w[p + "lq2"] * w[p + "lk2"]).sum())
            + m["diff"])
-    mask = visible(T)
+    mask = visible(T, (m.get("mask") or {}).get("size"))       # causal; a window only if the layer names one
     gate = torch.sigmoid(h @ w[p + "g"].T)                     # [T, H]
-    cap = m["softcap"]
+    cap = m.get("softcap")                                       # absent or null: the scores are not capped
     heads = []
     for hd in range(H):
         g = hd // (H // G)
         maps = []
         for which in range(2):
             s = (q[:, hd, which] @ k[:, g, which].T) * m["scale"]
-            s = cap * torch.tanh(s / cap)
+            if cap is not None:
+                s = cap * torch.tanh(s / cap)
             maps.append(softmax_over(s, mask) @ v[:, g])
         o = maps[0] - lam * maps[1]
         o = unit_rms(o, eps) * (1.0 - m["diff"])
@@ -158,7 +159,7 @@ def latent_attention(cfg, w, p, m, h, positions):
     qr = rotate_half_split(q[..., d:], positions, dr, base)                      # [T, H, dr]
     ku = (c @ w[p + "uk"].T).view(T, H, d)
     v = (c @ w[p + "uv"].T).view(T, H, dv)
-    mask = visible(T, m["mask"]["size"])
+    mask = visible(T, (m.get("mask") or {}).get("size"))
     gate = torch.sigmoid(h @ w[p + "g"].T)
     heads = []
     for hd in range(H):

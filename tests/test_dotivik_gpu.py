@@ -207,19 +207,25 @@ def test_stream_packing_and_gated_activation():
         torch.testing.assert_close(out.cpu().double(), (f(zs[:, :, 0]) * zs[:, :, 1]).reshape(T, 24), atol=2e-6, rtol=2e-6)
 
 
-def test_one_small_matrix_per_head_through_strided_views():
+@pytest.mark.parametrize("T,H,Kd,N,off,pad", [(37, 3, 20, 70, 3, 6), (150, 5, 96, 128, 8, 16), (70, 2, 40, 24, 0, 0)])
+def test_one_small_matrix_per_head_through_strided_views(T, H, Kd, N, off, pad):
+    """x and out are runs of columns of wider rows.  In bfloat16, strides and offsets that are multiples of 8
+    take the tensor-core kernel (K padded to 32 inside), the others the CUDA cores."""
     from mini_hisparse_b200.kernels import api as K
 
     g = torch.Generator().manual_seed(3)
-    T, H, Kd, N = 37, 3, 20, 70
-    wide_in, wide_out = torch.randn(T, H, Kd + 6, generator=g), torch.zeros(T, H, N + 5)
+    wide_in, wide_out = torch.randn(T, H, Kd + pad, generator=g), torch.zeros(T, H, N + 5)
     w = torch.randn(H, N, Kd, generator=g)
     for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2)):
         xi, wo = wide_in.to(dtype).cuda(), wide_out.to(dtype).cuda()
-        K.head_linear(xi[:, :, 3:3 + Kd], w.to(dtype).cuda(), wo[:, :, :N])
-        ref = torch.einsum("thk,hnk->thn", xi[:, :, 3:3 + Kd].double().cpu(), w.to(dtype).double())
+        K.head_linear(xi[:, :, off:off + Kd], w.to(dtype).cuda(), wo[:, :, :N])
+        ref = torch.einsum("thk,hnk->thn", xi[:, :, off:off + Kd].double().cpu(), w.to(dtype).double())
         torch.testing.assert_close(wo[:, :, :N].double().cpu(), ref, atol=tol * float(ref.abs().max()), rtol=0)
         assert float(wo[:, :, N:].abs().max()) == 0.0         # nothing beyond the view
+        if dtype == torch.bfloat16:                            # float32 out of bfloat16 operands
+            wf = torch.zeros(T, H, N, device="cuda")
+            K.head_linear(xi[:, :, off:off + Kd], w.to(dtype).cuda(), wf)
+            torch.testing.assert_close(wf.double().cpu(), ref, atol=1e-5 * float(ref.abs().max()), rtol=0)
 
 
 def plain_maps_attention(q, k, v, qpos, scale, cap, window=None):
@@ -296,7 +302,7 @@ def test_score_maps_far_keys_and_the_cap(dtype, kernel, page_size, H, G, d, dv, 
     table = torch.randperm(pages + 3, generator=g)[:pages].to(torch.int32)
     pool = torch.full((pages + 3, G * page_size * (M * d + dv)), 1e30).to(dtype).cuda()
     qw, kw, vw = H * M * d, G * M * d, G * dv
-    proj = torch.randn(2, L, qw + kw + vw + H + 3, generator=g)          # two split-K parts; the gates follow v
+    proj = torch.randn(2, L, qw + kw + vw + H + 3, generator=g) * 0.5 ** 0.5   # two split-K parts (unit sum); the gates follow v
     pos = torch.arange(L, dtype=torch.int32)
     inv = torch.tensor([100.0 ** (-2.0 * i / rdim) for i in range(rdim // 2)]) if rdim else None
     q_all = torch.empty(L, qw, dtype=dtype, device="cuda")
@@ -314,7 +320,8 @@ def test_score_maps_far_keys_and_the_cap(dtype, kernel, page_size, H, G, d, dv, 
     pk = pool.float().cpu().view(pages + 3, -1)[table.long()]
     got_k = pk[:, :G * page_size * M * d].reshape(pages, G, page_size, M, d).permute(0, 2, 1, 3, 4).reshape(-1, G, M, d)[:L]
     got_v = pk[:, G * page_size * M * d:].reshape(pages, G, page_size, dv).permute(0, 2, 1, 3).reshape(-1, G, dv)[:L]
-    tol = (2e-6 if L <= 400 else 2e-4) if dtype == torch.float32 else 0.02
+    # float32 angles: position times frequency is rounded to 24 bits, so far positions turn by up to 1e-4 radians less or more
+    tol = (5e-6 if L <= 400 else 2e-4) if dtype == torch.float32 else 0.02
     assert float((got_k.double() - kf).abs().max()) < tol * float(kf.abs().max())
     assert float((got_v.double() - vf).abs().max()) < tol * float(vf.abs().max())
     assert float((q_all.float().cpu().double().view(L, H, M, d) - qf).abs().max()) < tol * float(qf.abs().max())
@@ -398,7 +405,7 @@ def test_latent_rows_at_the_windows_edges(dtype, kernel, page_size, window, H, d
     table = torch.randperm(pages + 3, generator=g)[:pages].to(torch.int32)
     pool = torch.full((pages + 3, page_size, width), 1e30).to(dtype).cuda()
     qw = H * (d + dr)
-    proj = torch.randn(2, L, qw + width + H + 5, generator=g)
+    proj = torch.randn(2, L, qw + width + H + 5, generator=g) * 0.5 ** 0.5     # two split-K parts whose sum has unit variance
     cw = 1 + 0.1 * torch.randn(rank, generator=g)
     uk = torch.randn(H, d, rank, generator=g) / math.sqrt(d)          # k_h = uk[h] @ c ... stored [H * d, rank]
     pos = torch.arange(L, dtype=torch.int32)
@@ -417,12 +424,13 @@ def test_latent_rows_at_the_windows_edges(dtype, kernel, page_size, window, H, d
     kr = P.rotate_half_split(ps[:, None, qw + rank:qw + width], pos, dr, 100.0)[:, 0]
     rows_ref = torch.cat((c, kr), 1)
     got_rows = pool.float().cpu()[table.long()].reshape(-1, width)[:L].double()
-    tol = (2e-6 if L <= 400 else 2e-4) if dtype == torch.float32 else 0.02
+    # float32 angles: position times frequency is rounded to 24 bits, so far positions turn by up to 1e-4 radians less or more
+    tol = (5e-6 if L <= 400 else 2e-4) if dtype == torch.float32 else 0.02
     assert float((got_rows - rows_ref).abs().max()) < tol * float(rows_ref.abs().max())
     q_ref = torch.cat((torch.einsum("thd,hdr->thr", qh[..., :d], uk.to(dtype).double()),
                        P.rotate_half_split(qh[..., d:], pos, dr, 100.0)), -1)
     got_q = q_full.float().cpu().double()
-    assert float((got_q - q_ref).abs().max()) < (1e-5 if dtype == torch.float32 else 0.03) * float(q_ref.abs().max())
+    assert float((got_q - q_ref).abs().max()) < (max(tol, 1e-5) if dtype == torch.float32 else 0.03) * float(q_ref.abs().max())
     # the window's edges at the probe stand out in the cache
     rc = got_rows.clone()
     probe = L - 5
