@@ -268,7 +268,8 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_acc,
 
 template <typename CT>
 int launch_attention(const AttnArgs& a, int max_items, cudaStream_t stream) {
-    const int dpl = (a.dv + 31) / 32;
+    int dpl = (a.dv + 31) / 32;
+    if (dpl > 8) dpl = dpl <= 12 ? 12 : 16;      // wide values: accumulators for 384 or 512 elements per row
     const size_t smem = sizeof(float) * ((size_t)R_TILE * a.d + (size_t)KT * (a.d + 1) + (size_t)KT * a.dv);
     dim3 grid(max_items, a.nkv * a.kparts);
 #define MHB_ATTN_CASE(N)                                                                        \
@@ -286,7 +287,8 @@ int launch_attention(const AttnArgs& a, int max_items, cudaStream_t stream) {
     switch (dpl) {
         MHB_ATTN_CASE(1) MHB_ATTN_CASE(2) MHB_ATTN_CASE(3) MHB_ATTN_CASE(4)
         MHB_ATTN_CASE(5) MHB_ATTN_CASE(6) MHB_ATTN_CASE(7) MHB_ATTN_CASE(8)
-        default: return fail("attention: a value width of %d is larger than 256", a.dv);
+        MHB_ATTN_CASE(12) MHB_ATTN_CASE(16)
+        default: return fail("attention: a value width of %d is larger than 512", a.dv);
     }
 #undef MHB_ATTN_CASE
     return check_launch("attention_simt");

@@ -43,8 +43,8 @@ class LatentAttention(Mixer):
         if int(getattr(self.position, "rotary_dim", 0) or 0) != self.dr:
             raise ValueError(f"the position part must rotate all {self.dr} elements of the rotated key part")
         self.width = self.rank + self.dr                    # a cache row, and a query in the latent space
-        if self.rank > 256:
-            raise ValueError(f"a latent {self.rank} wide: the attention kernels take values up to 256 wide")
+        if self.rank > 512:
+            raise ValueError(f"a latent {self.rank} wide: the attention kernels take values up to 512 wide")
         self.qw, self.ow = self.heads * (self.d + self.dr), self.heads * self.dv
         self.weight = self.o_weight = self.c_norm = self.uk_t = self.uv = None
 

@@ -55,8 +55,8 @@ class DifferentialAttention(Mixer):
         self.window = spec.get("window")
         if self.heads % self.nkv:
             raise ValueError(f"{self.heads} query heads cannot be grouped over {self.nkv} KV heads")
-        if self.dv > 256:
-            raise ValueError(f"values {self.dv} wide: the attention kernels take up to 256")
+        if self.dv > 512:
+            raise ValueError(f"values {self.dv} wide: the attention kernels take up to 512")
         self.position = POSITIONS.build(spec["position"], rt=rt)
         self.nq = self.heads * MAPS                       # query maps: what the attention kernels call heads
         self.qw, self.kw, self.vw = self.nq * self.d, self.nkv * MAPS * self.d, self.nkv * self.dv

@@ -440,7 +440,8 @@ def test_latent_rows_at_the_windows_edges(dtype, kernel, page_size, window, H, d
         if p_ >= 0 and p_ != probe:
             qd = got_q[probe, 0]
             row = (qd * (score / (scale * float(qd @ qd)))).to(dtype).double()
-            row[:rank] += val                                  # the row is its own value: mark it
+            ones = torch.ones(rank, dtype=torch.float64)       # the row is its own value: mark it, across the query
+            row[:rank] += val * (ones - qd[:rank] * (float(ones @ qd[:rank]) / float(qd[:rank] @ qd[:rank])))
             row = row.to(dtype).double()
             rc[p_] = row
             pool[int(table[p_ // page_size]), p_ % page_size] = row.to(dtype).cuda()
