@@ -64,6 +64,9 @@ struct AttnArgs {
     const float* gate;
     int gate_nsplit, gate_ld;
     size_t gate_split_stride;
+    int gate_per_head;           // the gate has one column per head instead of one per output element
+    // a latent cache: a page holds [P][d] rows and nothing else (one KV head), and a row is key AND value
+    int shared_kv;
 };
 
 __device__ __forceinline__ float gate_of(const AttnArgs& a, int t, int col) {
@@ -197,7 +200,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
             if (lane == 0) mbar_expect_tx(full, __popc(have) * a.P * D * 2);
             __syncwarp();
             if (page >= 0) {
-                const int row0 = ((page * 2 + (values ? 1 : 0)) * a.nkv + kvh) * a.P;
+                const int row0 = (EXT && a.shared_kv) ? page * a.P : ((page * 2 + (values ? 1 : 0)) * a.nkv + kvh) * a.P;
                 const uint32_t dst = (values ? v_ring : k_ring) + stage * L::K_BYTES + lane * a.P * 128;
 #pragma unroll
                 for (int h = 0; h < HALVES; ++h) tma_load_2d(dst + h * KT * 128, &kv_map, h * 64, row0, full);
@@ -420,7 +423,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
                 }
                 if (gated) {
 #pragma unroll
-                    for (int x = 0; x < 16; ++x) r[x] = __float_as_uint(__uint_as_float(r[x]) * gate_of(a, t, hq * D + c + x));
+                    for (int x = 0; x < 16; ++x) r[x] = __float_as_uint(__uint_as_float(r[x]) * gate_of(a, t, a.gate_per_head ? hq : hq * D + c + x));
                 }
                 if (live) {
                     uint4 v0, v1;
@@ -487,23 +490,26 @@ MHB_EXPORT int mhb_attention_tc(const void* q, const void* cache, void* out, con
     a.status = status; a.num_items = num_items; a.width = width; a.nq = nq;
     a.nkv = nkv; a.P = P; a.num_pages = num_pages; a.window = window; a.scale = scale;
     a.sink = nullptr; a.gate = nullptr; a.gate_nsplit = 1; a.gate_ld = 0; a.gate_split_stride = 0;
+    a.gate_per_head = 0; a.shared_kv = 0;
     return d == 128 ? launch<128, false>(map, a, num_items, stream) : launch<64, false>(map, a, num_items, stream);
 }
 
 // The same with the options (see EXT at the kernel): a sink per query head, a gate on the output, softmax
-// weights that keep 16 bits in the value product.  Keys and values are both d wide here.
+// weights that keep 16 bits in the value product.  Keys and values are both d wide here.  shared_kv: the
+// pool is [num_pages, P, d] and every row is its position's key and value at once (a latent cache).
 MHB_EXPORT int mhb_attention_tc_ext(const void* q, const void* cache, void* out, const int* items, int num_items,
                                     const int* positions, const int* block_table, int width,
                                     const int* tok_part_row, float* part_acc, float* part_ml, int nq, int nkv, int d,
                                     int P, int num_pages, int window, float scale, const float* sink,
                                     const float* gate, int gate_nsplit, long long gate_split_stride, int gate_ld,
-                                    int* status, cudaStream_t stream) {
+                                    int gate_per_head, int shared_kv, int* status, cudaStream_t stream) {
     if (num_items <= 0) return 0;
     if (nkv <= 0 || nq % nkv) return fail("attention: %d query heads over %d KV heads", nq, nkv);
     if (!mhb_attention_tc_supports(d, P))
         return fail("attention_tc: head_dim %d with pages of %d keys is not built (head_dim 64 or 128, page size dividing 64)", d, P);
     if (sink && !(scale > 0.f)) return fail("attention_tc: a sink needs a positive scale");
-    const long long total_rows = (long long)num_pages * 2 * nkv * P;
+    if (shared_kv && nkv != 1) return fail("attention_tc: rows that are key and value at once have one KV head");
+    const long long total_rows = shared_kv ? (long long)num_pages * P : (long long)num_pages * 2 * nkv * P;
     if (total_rows > 0x7fffffffLL) return fail("attention_tc: the pool has too many rows for one tensor map");
     CUtensorMap map;
     int rc = make_bf16_map(&map, cache, total_rows, d, d, P);
@@ -515,5 +521,6 @@ MHB_EXPORT int mhb_attention_tc_ext(const void* q, const void* cache, void* out,
     a.nkv = nkv; a.P = P; a.num_pages = num_pages; a.window = window; a.scale = scale;
     a.sink = sink; a.gate = gate; a.gate_nsplit = gate_nsplit; a.gate_ld = gate_ld;
     a.gate_split_stride = (size_t)gate_split_stride;
+    a.gate_per_head = gate_per_head; a.shared_kv = shared_kv;
     return d == 128 ? launch<128, true>(map, a, num_items, stream) : launch<64, true>(map, a, num_items, stream);
 }

@@ -689,9 +689,10 @@ def attention_tma_ext(q, cache, out, part_acc, part_ml, items, num_items, rows, 
 
 def attention_tc_ext(q, cache, out, items, num_items, positions, block_table, *, nq, nkv, d, page_size,
                      window=0, scale=None, status=None, part_acc=None, part_ml=None, tok_part_row=None,
-                     sink=None, gate=None, gate_nsplit=1, gate_split_stride=0):
-    """attention_tc with a ``sink`` per query head, a ``gate`` on the output and softmax weights that keep 16
-    bits in the value product; keys and values are both ``d`` wide."""
+                     sink=None, gate=None, gate_nsplit=1, gate_split_stride=0, gate_per_head=False, shared_kv=False):
+    """attention_tc with a ``sink`` per query head, a ``gate`` on the output (``gate_per_head``: one column
+    per head) and softmax weights that keep 16 bits in the value product; keys and values are both ``d``
+    wide.  ``shared_kv``: the pool is [pages, P, d] and a row is its position's key and value at once."""
     lib = build.load("attention_tc")
     if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or not cache.is_contiguous():
         raise KernelError("attention_tc_ext: q and the (contiguous) pool must be bfloat16")
@@ -702,7 +703,8 @@ def attention_tc_ext(q, cache, out, items, num_items, positions, block_table, *,
         _ptr(q), _ptr(cache), _ptr(out), _ptr(items), c_int(num_items), _ptr(positions), _ptr(block_table),
         c_int(block_table.shape[-1]), _ptr(tok_part_row), _ptr(part_acc), _ptr(part_ml),
         c_int(nq), c_int(nkv), c_int(d), c_int(page_size), c_int(cache.shape[0]), c_int(window or 0),
-        c_float(scale), _ptr(sink), g[0], g[1], g[2], g[3], _ptr(status), _stream()), "attention_tc_ext")
+        c_float(scale), _ptr(sink), g[0], g[1], g[2], g[3], c_int(1 if gate_per_head else 0),
+        c_int(1 if shared_kv else 0), _ptr(status), _stream()), "attention_tc_ext")
 
 
 def attention_combine(part_acc, part_ml, tok_part_row, tok_nsplit, out, *, nq, d, every=0, gate=None,

@@ -49,26 +49,38 @@ class LatentAttention(Mixer):
         self.weight = self.o_weight = self.c_norm = self.uk_t = self.uv = None
 
     def kernel_family(self, page_size: int | None = None) -> str:
-        """"mma": mma.sync tiles (bfloat16, a cache row of at most 128 elements, a multiple of 8 like the
-        latent); "simt": the CUDA cores (float32, and every other width)."""
+        """"tc": tcgen05 128-row tiles for long portions (bfloat16, a cache row 64 or 128 wide, pages that divide
+        64) and mma.sync 16-row tiles for the rest; "mma": mma.sync tiles of 64 and 16 rows (bfloat16, a cache
+        row of at most 128 elements, a multiple of 8 like the latent); "simt": the CUDA cores (float32, and every
+        other width)."""
         if (self.rt is None or self.rt.dtype != torch.bfloat16 or not self.scale > 0.0
                 or not K.attention_mma_ext_supports(self.width, self.rank)):
             return "simt"
-        return "mma" if K.MMA_EXT_GENERAL else "simt"
+        if page_size is not None and self.width in (64, 128) and K.attention_tma_supports(self.width, page_size):
+            return "tc"
+        return "mma"
+
+    def value_width(self, page_size: int | None) -> int:
+        """How much of a cache row the attention kernels take as the value: the latent; in the "tc" family the
+        whole row (its tiles have keys and values of one width; the columns behind the latent are not read
+        afterwards)."""
+        return self.width if self.kernel_family(page_size) == "tc" else self.rank
 
     def kernel_modules(self):
         if self.kernel_family() == "simt":
             return ("attention_simt", "mixparts")
+        if self.width in (64, 128):
+            return ("attention_simt", "attention_mma_ext", "attention_tc", "mixparts")
         return ("attention_simt", "attention_mma_ext", "mixparts")
 
     def cache_need(self):
         return PagedRowsNeed(width=self.width, window=self.window)
 
     def plan_key(self):
-        return ("latent_attention", self.heads, self.window, self.kernel_family())
+        return ("latent_attention", self.heads, self.window, self.width, self.rt is not None and self.rt.dtype)
 
     def planner(self, page_size: int, sm_count: int):
-        rows = {"mma": 64, "simt": ROW_TILE}[self.kernel_family(page_size)]
+        rows = {"tc": 128, "mma": 64, "simt": ROW_TILE}[self.kernel_family(page_size)]
         return AttentionPlanner(AttentionShape(self.heads, 1, self.window, rows), sm_count)
 
     def parameters(self):
@@ -102,30 +114,41 @@ class LatentAttention(Mixer):
         g0 = self.qw + self.width
         gate = dict(gate=(p[0] if proj.nsplit > 1 else p)[:, g0:g0 + self.heads], gate_nsplit=proj.nsplit,
                     gate_split_stride=proj.split_stride, gate_per_head=True)
-        lat = ws.get("la_out", (T, self.heads, self.rank), rt.dtype)              # sum_j p_j c_j, gated
+        family = self.kernel_family(cache.page_size)
+        vw = self.value_width(cache.page_size)
+        lat = ws.get("la_out", (T, self.heads, vw), rt.dtype)                     # sum_j p_j c_j, gated
         part_rows = max(1, meta["part_rows_cap"])
-        part_acc = ws.get("attn_part_acc", (part_rows, self.heads, self.rank), torch.float32)
+        part_acc = ws.get("attn_part_acc", (part_rows, self.heads, vw), torch.float32)
         part_ml = ws.get("attn_part_ml", (part_rows, self.heads, 2), torch.float32)
         n_small, n_big = meta["n_small"], meta["n_big"]
-        common = dict(nq=self.heads, nkv=1, d=self.width, dv=self.rank, page_size=cache.page_size,
+        common = dict(nq=self.heads, nkv=1, d=self.width, dv=vw, page_size=cache.page_size,
                       window=self.window or 0, scale=self.scale, shared_kv=True, **gate)
         args = (q_full, cache.storage, lat, part_acc, part_ml)
         tail = (ctx.positions, meta["block_table"], meta["tok_part_row"])
-        if self.kernel_family(cache.page_size) == "mma":
-            if n_small:
+        if family != "simt":
+            if n_small:          # decoded tokens and short portions: 16-row tiles, key splits merged by the last CTA
                 chunks = -(-self.heads // ROW_TILE)
                 counters = ws.get_zeroed("attn_counters", (T * chunks,), torch.int32)
                 K.attention_mma_ext(*args, meta["items"], n_small, 16, *tail, **common,
                                     tok_nsplit=meta["tok_nsplit"], counters=counters)
-            if n_big:
-                K.attention_mma_ext(*args, meta["items"][n_small * ITEM_INTS:], n_big, 64, *tail, **common)
+            big_items = meta["items"][n_small * ITEM_INTS:]
+            if n_big and family == "tc":      # long portions: tcgen05 128-row tiles, split along the keys when few
+                K.attention_tc_ext(q_full, cache.storage, lat, big_items, n_big, ctx.positions, meta["block_table"],
+                                   nq=self.heads, nkv=1, d=self.width, page_size=cache.page_size,
+                                   window=self.window or 0, scale=self.scale, status=ctx.status, part_acc=part_acc,
+                                   part_ml=part_ml, tok_part_row=meta["tok_part_row"], shared_kv=True, **gate)
+                if meta.get("big_split"):
+                    K.attention_combine(part_acc, part_ml, meta["tok_part_row"], meta["tok_nsplit"], lat,
+                                        nq=self.heads, d=vw, **gate)
+            elif n_big:          # long portions: 64-row tiles
+                K.attention_mma_ext(*args, big_items, n_big, 64, *tail, **common)
         else:
             n = n_small + n_big
             if n:
                 K.attention_simt(*args, meta["items"], n, n, *tail, **common)
             if meta["any_split"]:
                 K.attention_combine(part_acc, part_ml, meta["tok_part_row"], meta["tok_nsplit"], lat, nq=self.heads,
-                                    d=self.rank, **gate)
+                                    d=vw, **gate)
         attn = ws.get("la_attn", (T, self.heads, self.dv), rt.dtype)
-        K.head_linear(lat, self.uv, attn)
+        K.head_linear(lat[:, :, :self.rank], self.uv, attn)
         return rt.linear(attn.view(T, self.ow), self.o_weight, ws, "mix_out", out_dtype=torch.float32)

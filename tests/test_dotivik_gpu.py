@@ -261,15 +261,23 @@ def attend(K, kernel, dtype, shape, segments, q_rows, pool, table, out_shape, ou
     positions = dev_i(torch.cat([torch.arange(s.start, s.start + s.count) for s in segments]))
     items = dev_i(torch.from_numpy(plan.items))
     tpr, tns = dev_i(torch.from_numpy(plan.tok_part_row)), dev_i(torch.from_numpy(plan.tok_nsplit))
-    gate = {k: opts[k] for k in ("gate", "gate_per_head") if k in opts}
-    if kernel == "mma":
+    gate = {k: opts[k] for k in ("gate", "gate_nsplit", "gate_split_stride", "gate_per_head") if k in opts}
+    if kernel in ("mma", "tc"):
         if plan.n_small:
             counters = torch.zeros(T * opts["nkv"] * opts.get("kparts", 1) * -(-(shape.q_heads // shape.kv_heads) // 16),
                                    dtype=torch.int32, device="cuda")
             K.attention_mma_ext(q_rows, pool, o, part_acc, part_ml, items, plan.n_small, 16, positions, tables, tpr,
                                 **opts, tok_nsplit=tns, counters=counters)
             assert int(counters.abs().sum()) == 0
-        if plan.n_big:
+        if plan.n_big and kernel == "tc":
+            status = torch.zeros(1, dtype=torch.int32, device="cuda")
+            tc = {k: v for k, v in opts.items() if k not in ("dv", "kparts", "softcap")}
+            K.attention_tc_ext(q_rows, pool, o, items.view(-1)[plan.n_small * 8:], plan.n_big, positions, tables,
+                               status=status, part_acc=part_acc, part_ml=part_ml, tok_part_row=tpr, **tc)
+            assert int(status) == 0
+            if plan.big_split:
+                K.attention_combine(part_acc, part_ml, tpr, tns, o, nq=nq, d=dv, **gate)
+        elif plan.n_big:
             K.attention_mma_ext(q_rows, pool, o, part_acc, part_ml, items.view(-1)[plan.n_small * 8:], plan.n_big, 64,
                                 positions, tables, tpr, **opts)
     else:
@@ -380,9 +388,11 @@ def test_score_maps_far_keys_and_the_cap(dtype, kernel, page_size, H, G, d, dv, 
         (3e-6 if dtype == torch.float32 else 0.01) * float(ref.abs().max())
 
 
-@pytest.mark.parametrize("dtype,kernel", [(torch.float32, "simt"), (torch.bfloat16, "simt"), (torch.bfloat16, "mma")])
+@pytest.mark.parametrize("dtype,kernel", [(torch.float32, "simt"), (torch.bfloat16, "simt"), (torch.bfloat16, "mma"),
+                                          (torch.bfloat16, "tc")])
 @pytest.mark.parametrize("page_size,window,H,d,dr,rank", [(16, 48, 4, 24, 8, 40), (8, 33, 20, 16, 16, 32), (16, 300, 3, 12, 4, 12),
-                                                          (32, 150, 8, 64, 32, 96), (16, 1150, 2, 32, 16, 64), (16, 1, 2, 8, 2, 24)])
+                                                          (32, 150, 8, 64, 32, 96), (16, 1150, 2, 32, 16, 64), (16, 1, 2, 8, 2, 24),
+                                                          (16, 90, 40, 16, 16, 48), (16, 1150, 4, 64, 32, 96)])
 def test_latent_rows_at_the_windows_edges(dtype, kernel, page_size, window, H, d, dr, rank):
     """The latent rows go through their kernel (unit norm with weight, the shared key part rotated) into shuffled
     pages in two steps, q's unrotated parts are carried into the latent space by one small matrix per head; then a
@@ -396,6 +406,9 @@ def test_latent_rows_at_the_windows_edges(dtype, kernel, page_size, window, H, d
     width = rank + dr
     if kernel == "mma" and not K.attention_mma_ext_supports(width, rank):
         pytest.skip("widths the tensor-core attention does not take")
+    if kernel == "tc" and not (width in (64, 128) and K.attention_tma_supports(width, page_size)):
+        pytest.skip("the tcgen05 kernel takes rows 64 or 128 wide over pages that divide 64")
+    vw = width if kernel == "tc" else rank          # the tcgen05 tiles take the whole row as the value
     g = torch.Generator().manual_seed(5)
     L = 200 if window < 1000 else 1300
     scale = 2.2 / math.sqrt(width)
@@ -457,7 +470,7 @@ def test_latent_rows_at_the_windows_edges(dtype, kernel, page_size, window, H, d
         for wrong in (plain(window + 1), plain(window - 1)):
             assert float((wrong[probe] - right[probe]).abs().max()) > 0.2
     g0 = qw + width
-    shape = AttentionShape(H, 1, window, {"mma": 64, "simt": 16}[kernel])
+    shape = AttentionShape(H, 1, window, {"tc": 128, "mma": 64, "simt": 16}[kernel])
     bound = 3e-6 if dtype == torch.float32 else 0.02
     for seg, rows in ((Segment("a", 0, L - portion, portion, 0), torch.arange(L - portion, L)),
                       (Segment("a", 0, L - 9, 9, 0), torch.arange(L - 9, L)),
@@ -465,11 +478,13 @@ def test_latent_rows_at_the_windows_edges(dtype, kernel, page_size, window, H, d
                       (Segment("a", 0, L - 1, 1, 0), torch.tensor([L - 1])),
                       (Segment("a", 0, 0, 20, 0), torch.arange(0, 20))):
         gates = proj[:, rows][:, :, g0:g0 + H].contiguous().cuda()
-        opts = dict(nq=H, nkv=1, d=width, dv=rank, page_size=page_size, window=window, scale=scale, shared_kv=True,
+        opts = dict(nq=H, nkv=1, d=width, dv=vw, page_size=page_size, window=window, scale=scale, shared_kv=True,
                     gate=gates[0], gate_nsplit=2, gate_split_stride=gates.stride(0), gate_per_head=True)
-        got, _ = attend(K, kernel, dtype, shape, [seg], q_full[rows].contiguous(), pool, table, (H, rank), dtype, **opts)
+        got, plan = attend(K, kernel, dtype, shape, [seg], q_full[rows].contiguous(), pool, table, (H, vw), dtype, **opts)
+        if kernel == "tc" and window > 1000 and seg.count > 16:
+            assert plan.big_split                     # few tiles far into a long window: their keys are split
         ref = right[rows] * torch.sigmoid(gates.double().sum(0).cpu())[:, :, None]
-        assert float((got - ref).abs().max()) < bound * float(right.abs().max())
+        assert float((got[..., :rank] - ref).abs().max()) < bound * float(right.abs().max())
 
 
 # ---- the model through the step function -----------------------------------------------------------------
