@@ -67,6 +67,8 @@ struct AttnArgs {
     int gate_per_head;           // the gate has one column per head instead of one per output element
     // a latent cache: a page holds [P][d] rows and nothing else (one KV head), and a row is key AND value
     int shared_kv;
+    float softcap;               // s <- softcap * tanh(s / softcap) on the scaled score (0: none)
+    int out_f32;                 // `out` is float32 (a sum of the outputs is still to be taken in 32 bits)
 };
 
 __device__ __forceinline__ float gate_of(const AttnArgs& a, int t, int col) {
@@ -309,6 +311,19 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
             uint32_t sr[KT];
             tmem_ld64(lane_addr + (j & 1) * KT, sr);
             tmem_ld_wait();
+            if constexpr (EXT) {
+                if (a.softcap > 0.f) {
+                    // the cap works on the scaled score and the tile stays in the raw products' units:
+                    // s <- (cap / scale) tanh(s scale / cap), with tanh(x) = 1 - 2 / (1 + 2^(2 x log2 e)): an
+                    // exponential and a division of the special-function unit, absolute error of a few 2^-24
+                    const float k2 = 2.885390081777927f * a.scale / a.softcap, back = a.softcap / a.scale;
+#pragma unroll
+                    for (int x = 0; x < KT; ++x) {
+                        const float e = fast_exp2(__uint_as_float(sr[x]) * k2);
+                        sr[x] = __float_as_uint(back * (1.f - __fdividef(2.f, 1.f + e)));
+                    }
+                }
+            }
             const int t0 = tile_begin + j * KT;
             // most tiles lie wholly inside this row's range of keys: no mask then
             const int lo = max(kv_begin, a.window > 0 ? qp - a.window + 1 : 0), hi = min(kv_end - 1, qp);
@@ -425,7 +440,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
 #pragma unroll
                     for (int x = 0; x < 16; ++x) r[x] = __float_as_uint(__uint_as_float(r[x]) * gate_of(a, t, a.gate_per_head ? hq : hq * D + c + x));
                 }
-                if (live) {
+                if (EXT && a.out_f32) {
+                    if (live) {
+                        float* dstf = (float*)a.out + ((size_t)t * a.nq + hq) * D + c;
+#pragma unroll
+                        for (int x = 0; x < 16; x += 4)
+                            *(float4*)(dstf + x) = make_float4(__uint_as_float(r[x]) * inv, __uint_as_float(r[x + 1]) * inv,
+                                                               __uint_as_float(r[x + 2]) * inv, __uint_as_float(r[x + 3]) * inv);
+                    }
+                } else if (live) {
                     uint4 v0, v1;
                     v0.x = pack_bf16(__uint_as_float(r[0]) * inv, __uint_as_float(r[1]) * inv);
                     v0.y = pack_bf16(__uint_as_float(r[2]) * inv, __uint_as_float(r[3]) * inv);
@@ -490,19 +513,21 @@ MHB_EXPORT int mhb_attention_tc(const void* q, const void* cache, void* out, con
     a.status = status; a.num_items = num_items; a.width = width; a.nq = nq;
     a.nkv = nkv; a.P = P; a.num_pages = num_pages; a.window = window; a.scale = scale;
     a.sink = nullptr; a.gate = nullptr; a.gate_nsplit = 1; a.gate_ld = 0; a.gate_split_stride = 0;
-    a.gate_per_head = 0; a.shared_kv = 0;
+    a.gate_per_head = 0; a.shared_kv = 0; a.softcap = 0.f; a.out_f32 = 0;
     return d == 128 ? launch<128, false>(map, a, num_items, stream) : launch<64, false>(map, a, num_items, stream);
 }
 
 // The same with the options (see EXT at the kernel): a sink per query head, a gate on the output, softmax
 // weights that keep 16 bits in the value product.  Keys and values are both d wide here.  shared_kv: the
 // pool is [num_pages, P, d] and every row is its position's key and value at once (a latent cache).
+// softcap caps the scaled scores; out_f32 writes float32 outputs.
 MHB_EXPORT int mhb_attention_tc_ext(const void* q, const void* cache, void* out, const int* items, int num_items,
                                     const int* positions, const int* block_table, int width,
                                     const int* tok_part_row, float* part_acc, float* part_ml, int nq, int nkv, int d,
                                     int P, int num_pages, int window, float scale, const float* sink,
                                     const float* gate, int gate_nsplit, long long gate_split_stride, int gate_ld,
-                                    int gate_per_head, int shared_kv, int* status, cudaStream_t stream) {
+                                    int gate_per_head, int shared_kv, float softcap, int out_f32, int* status,
+                                    cudaStream_t stream) {
     if (num_items <= 0) return 0;
     if (nkv <= 0 || nq % nkv) return fail("attention: %d query heads over %d KV heads", nq, nkv);
     if (!mhb_attention_tc_supports(d, P))
@@ -521,6 +546,6 @@ MHB_EXPORT int mhb_attention_tc_ext(const void* q, const void* cache, void* out,
     a.nkv = nkv; a.P = P; a.num_pages = num_pages; a.window = window; a.scale = scale;
     a.sink = sink; a.gate = gate; a.gate_nsplit = gate_nsplit; a.gate_ld = gate_ld;
     a.gate_split_stride = (size_t)gate_split_stride;
-    a.gate_per_head = gate_per_head; a.shared_kv = shared_kv;
+    a.gate_per_head = gate_per_head; a.shared_kv = shared_kv; a.softcap = softcap; a.out_f32 = out_f32;
     return d == 128 ? launch<128, true>(map, a, num_items, stream) : launch<64, true>(map, a, num_items, stream);
 }

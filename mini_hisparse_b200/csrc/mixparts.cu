@@ -138,7 +138,7 @@ __global__ void rope_append_maps_kernel(const float* __restrict__ proj, int nspl
                                         const int* __restrict__ block_table, int table_width,
                                         const float* __restrict__ inv_freq, int rdim, int interleaved,
                                         QT* __restrict__ q_out, CT* __restrict__ cache, int nq, int nkv, int kparts,
-                                        int d, int dv, int P, int num_pages, int* __restrict__ status) {
+                                        int d, int dv, int P, int num_pages, int q_pad, int* __restrict__ status) {
     extern __shared__ float sh[];            // cos, sin
     pdl_launch_dependents();
     pdl_wait();
@@ -170,7 +170,10 @@ __global__ void rope_append_maps_kernel(const float* __restrict__ proj, int nspl
     for (int idx = threadIdx.x; idx < (nq + kmaps) * units; idx += blockDim.x) {
         const int head = idx / units, u = idx - head * units;
         const size_t src = base + (size_t)head * d;      // the k maps follow the q maps in the row
-        QT* qdst = head < nq ? q_out + (size_t)t * qw + head * d : nullptr;
+        // q_pad: a q map is a row kparts * d wide that holds the map at its own columns (zeros elsewhere, below)
+        QT* qdst = head >= nq ? nullptr
+                   : q_pad ? q_out + ((size_t)t * nq + head) * (kparts * d) + (head % kparts) * d
+                           : q_out + (size_t)t * qw + head * d;
         CT* kdst = nullptr;
         if (head >= nq && page_k) {
             const int km = head - nq, g = km / kparts, m = km - g * kparts;
@@ -190,6 +193,14 @@ __global__ void rope_append_maps_kernel(const float* __restrict__ proj, int nspl
             const float a = load_parts(proj, src + e, nsplit, split_stride);
             if (qdst) qdst[e] = from_float<QT>(a);
             else kdst[e] = from_float<CT>(a);
+        }
+    }
+    if (q_pad) {
+        const int other = (kparts - 1) * d;           // the columns of a padded row that belong to other maps
+        for (int idx = threadIdx.x; idx < nq * other; idx += blockDim.x) {
+            const int head = idx / other, e = idx - head * other;
+            const int col = e < (head % kparts) * d ? e : e + d;
+            q_out[((size_t)t * nq + head) * (kparts * d) + col] = from_float<QT>(0.f);
         }
     }
     if (page_v) {
@@ -501,7 +512,7 @@ MHB_EXPORT int mhb_rope_append_maps(const float* proj, int nsplit, long long spl
                                     const int* positions, const int* tok_seg, const int* block_table, int table_width,
                                     const float* inv_freq, int rdim, int interleaved, void* q_out, void* cache,
                                     int dtype, int T, int nq, int nkv, int kparts, int d, int dv, int P, int num_pages,
-                                    int* status, cudaStream_t stream) {
+                                    int q_pad, int* status, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (rdim % 2 || rdim < 0 || rdim > d) return fail("rope_append_maps: %d rotated elements of %d", rdim, d);
     if (nq * d + nkv * kparts * d + nkv * dv > ld)
@@ -511,7 +522,7 @@ MHB_EXPORT int mhb_rope_append_maps(const float* proj, int nsplit, long long spl
     MHB_DISPATCH_DTYPE(dtype, CT,
         launch_kernel(rope_append_maps_kernel<CT, CT>, dim3(T), dim3(threads), smem, stream, proj, nsplit,
                       (size_t)split_stride, ld, positions, tok_seg, block_table, table_width, inv_freq, rdim,
-                      interleaved, (CT*)q_out, (CT*)cache, nq, nkv, kparts, d, dv, P, num_pages, status));
+                      interleaved, (CT*)q_out, (CT*)cache, nq, nkv, kparts, d, dv, P, num_pages, q_pad, status));
     return check_launch("rope_append_maps");
 }
 

@@ -14,6 +14,7 @@ CUDA graph captured for its batch size; only the packed buffer changes between r
 from __future__ import annotations
 
 import gc
+import os
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -332,6 +333,9 @@ class ModelRunner:
         self.observer = None
         self.side_stream = None
         self.side_events = None
+        self.branch_stream = None
+        self.branch_events = None
+        self.branch_streams = os.environ.get("MHB_BRANCH_STREAMS", "1") != "0"     # 0: blocks run their sublayers in turn
         self.stats = {"steps": 0, "tokens": 0, "graph_steps": 0, "graph_captures": 0, "two_stream_layers": 0,
                       "prepared_steps": 0, "graph_deferred": 0}
         self._ahead = None      # index arrays of the next decode step, packed while the GPU ran this one
@@ -406,6 +410,14 @@ class ModelRunner:
                 self.side_events = (torch.cuda.Event(), torch.cuda.Event())
             ctx.extras["side_stream"] = self.side_stream
             ctx.extras["side_events"] = self.side_events
+        if self.branch_streams:
+            # a second stream for blocks whose sublayers do not depend on one another (a parallel block's mixer
+            # and feed-forward in a step of few tokens); inside a graph capture it becomes a branch of the graph
+            if self.branch_stream is None:
+                self.branch_stream = torch.cuda.Stream(self.device)
+                self.branch_events = (torch.cuda.Event(), torch.cuda.Event())
+            ctx.extras["branch_stream"] = self.branch_stream
+            ctx.extras["branch_events"] = self.branch_events
         caches = self._cache_views(views)
         with K.stream_scope():
             out = self.model.forward(ctx, caches, views["rows"], observer=self.observer)

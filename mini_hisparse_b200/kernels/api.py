@@ -689,10 +689,12 @@ def attention_tma_ext(q, cache, out, part_acc, part_ml, items, num_items, rows, 
 
 def attention_tc_ext(q, cache, out, items, num_items, positions, block_table, *, nq, nkv, d, page_size,
                      window=0, scale=None, status=None, part_acc=None, part_ml=None, tok_part_row=None,
-                     sink=None, gate=None, gate_nsplit=1, gate_split_stride=0, gate_per_head=False, shared_kv=False):
+                     sink=None, gate=None, gate_nsplit=1, gate_split_stride=0, gate_per_head=False, shared_kv=False,
+                     softcap=0.0):
     """attention_tc with a ``sink`` per query head, a ``gate`` on the output (``gate_per_head``: one column
     per head) and softmax weights that keep 16 bits in the value product; keys and values are both ``d``
-    wide.  ``shared_kv``: the pool is [pages, P, d] and a row is its position's key and value at once."""
+    wide.  ``shared_kv``: the pool is [pages, P, d] and a row is its position's key and value at once;
+    ``softcap`` caps the scaled scores; ``out`` may be float32."""
     lib = build.load("attention_tc")
     if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or not cache.is_contiguous():
         raise KernelError("attention_tc_ext: q and the (contiguous) pool must be bfloat16")
@@ -704,7 +706,8 @@ def attention_tc_ext(q, cache, out, items, num_items, positions, block_table, *,
         c_int(block_table.shape[-1]), _ptr(tok_part_row), _ptr(part_acc), _ptr(part_ml),
         c_int(nq), c_int(nkv), c_int(d), c_int(page_size), c_int(cache.shape[0]), c_int(window or 0),
         c_float(scale), _ptr(sink), g[0], g[1], g[2], g[3], c_int(1 if gate_per_head else 0),
-        c_int(1 if shared_kv else 0), _ptr(status), _stream()), "attention_tc_ext")
+        c_int(1 if shared_kv else 0), c_float(softcap or 0.0), c_int(1 if out.dtype == torch.float32 else 0),
+        _ptr(status), _stream()), "attention_tc_ext")
 
 
 def attention_combine(part_acc, part_ml, tok_part_row, tok_nsplit, out, *, nq, d, every=0, gate=None,
@@ -796,10 +799,12 @@ def glu_act(gate_up, out, act: str, nsplit=1, split_stride=0, block=None):
 
 
 def rope_append_maps(proj, positions, tok_seg, block_table, inv_freq, rotary_dim, interleaved, q_out, cache, *,
-                     nq, nkv, kparts, d, dv, page_size, nsplit=1, split_stride=0, status=None):
+                     nq, nkv, kparts, d, dv, page_size, nsplit=1, split_stride=0, status=None, q_pad=False):
     """Rows of the float32 product [q: nq * d | k: nkv * kparts * d | v: nkv * dv | ...]: the first
     ``rotary_dim`` elements of every q and k map are rotated, q goes to ``q_out`` [T, nq * d], keys and values
-    into the page of the position ([keys: nkv][P][kparts * d] then [values: nkv][P][dv])."""
+    into the page of the position ([keys: nkv][P][kparts * d] then [values: nkv][P][dv]).  ``q_pad``: every q map
+    is written as a row as wide as a KV head's key row, [T, nq, kparts * d], at the columns of its own map, zeros
+    elsewhere: its product with the whole key row is the map's score."""
     lib = build.load("mixparts")
     T = q_out.shape[0]
     if proj.dtype != torch.float32 or cache.dtype != q_out.dtype:
@@ -810,8 +815,8 @@ def rope_append_maps(proj, positions, tok_seg, block_table, inv_freq, rotary_dim
         _ptr(proj), c_int(nsplit), c_longlong(split_stride), c_int(proj.stride(-2)), _ptr(positions), _ptr(tok_seg),
         _ptr(block_table), c_int(block_table.shape[-1]), _ptr(inv_freq), c_int(rotary_dim or 0),
         c_int(1 if interleaved else 0), _ptr(q_out), _ptr(cache), c_int(dtype_code(q_out.dtype)), c_int(T), c_int(nq),
-        c_int(nkv), c_int(kparts), c_int(d), c_int(dv), c_int(page_size), c_int(cache.shape[0]), _ptr(status),
-        _stream()), "rope_append_maps")
+        c_int(nkv), c_int(kparts), c_int(d), c_int(dv), c_int(page_size), c_int(cache.shape[0]),
+        c_int(1 if q_pad else 0), _ptr(status), _stream()), "rope_append_maps")
 
 
 def latent_prep(proj, weight, eps, positions, tok_seg, block_table, inv_freq, interleaved, q_plain, q_full, cache, *,

@@ -1,6 +1,8 @@
 """Block arrangements: how a layer's norms, mixer and feed-forward are wired to the residual."""
 from __future__ import annotations
 
+import torch
+
 from ..kernels import api as K
 from .base import Block, CacheView, Product, StepContext
 from .registry import FEED_FORWARDS, MIXERS, NORMS, register_block
@@ -119,10 +121,30 @@ class ParallelBlock(Block):
             out["feed_forward"] = self.feed_forward
         return out
 
+    #: up to this many tokens the two sublayers run side by side on two streams (see forward)
+    BRANCH_MAX_TOKENS = 64
+
     def forward(self, x, pending: Product | None, ctx: StepContext, cache: CacheView | None) -> Product:
         h = self.norm.forward(x, ctx, delta=pending)
-        a = self.mixer.forward(h, ctx, cache)
         if self.feed_forward is None:
-            return a
-        f = self.feed_forward.forward(h, ctx)
+            return self.mixer.forward(h, ctx, cache)
+        branch = ctx.extras.get("branch_stream") if h.shape[0] <= self.BRANCH_MAX_TOKENS else None
+        if branch is None:
+            a = self.mixer.forward(h, ctx, cache)
+            f = self.feed_forward.forward(h, ctx)
+            return Product(a.tensor, a.nsplit, also=f)
+        # A step of few tokens (decoding): the feed-forward streams most of the layer's weights while the
+        # mixer is a chain of small kernels that wait for one another; the two read the same h and write
+        # buffers of their own, so the feed-forward runs on a second stream beside the mixer (in a captured
+        # graph: two branches of the graph) and the next norm waits for both.  Only for few tokens: their
+        # products are the ones that need no scratch shared between launches.
+        main = torch.cuda.current_stream()
+        fork, join = ctx.extras["branch_events"]
+        fork.record(main)
+        branch.wait_event(fork)
+        with torch.cuda.stream(branch), K.stream_scope():
+            f = self.feed_forward.forward(h, ctx)
+            join.record(branch)
+        a = self.mixer.forward(h, ctx, cache)
+        main.wait_event(join)
         return Product(a.tensor, a.nsplit, also=f)

@@ -65,25 +65,38 @@ class DifferentialAttention(Mixer):
         self.lam = None
 
     def kernel_family(self, page_size: int | None = None) -> str:
-        """"mma": mma.sync tiles of 64 and 16 rows (bfloat16, widths that are multiples of 8 up to 128);
-        "simt": the CUDA cores (float32, and every other width)."""
-        if self.rt is None or self.rt.dtype != torch.bfloat16 or not K.attention_mma_ext_supports(self.d, self.dv):
+        """"tc": the two maps' keys of a KV head lie side by side and are as wide together as its values (64 or 128,
+        bfloat16, pages that divide 64): every q map is padded with zeros to that width, at its own map's columns,
+        so a map's score is the product with the WHOLE key row and the kernels see plain grouped-query attention
+        with 2 x heads query heads: tcgen05 128-row tiles for long portions, mma.sync 16-row tiles for the rest.
+        "mma": mma.sync tiles of 64 and 16 rows that read a map's keys at its columns (bfloat16, widths that are
+        multiples of 8 up to 128); "simt": the CUDA cores (float32, and every other width)."""
+        if (self.rt is None or self.rt.dtype != torch.bfloat16 or not self.scale > 0.0
+                or not K.attention_mma_ext_supports(self.d, self.dv)):
             return "simt"
-        return "mma" if K.MMA_EXT_GENERAL else "simt" if self.scale > 0.0 else "simt"
+        if (page_size is not None and MAPS * self.d == self.dv and self.dv in (64, 128)
+                and K.attention_tma_supports(self.dv, page_size)):
+            return "tc"
+        return "mma"
 
     def kernel_modules(self):
         if self.kernel_family() == "simt":
             return ("attention_simt", "mixparts")
+        if MAPS * self.d == self.dv and self.dv in (64, 128):
+            return ("attention_simt", "attention_mma_ext", "attention_tc", "mixparts")
         return ("attention_simt", "attention_mma_ext", "mixparts")
 
     def cache_need(self):
         return PagedKVNeed(kv_heads=self.nkv, head_dim=MAPS * self.d, window=self.window, v_dim=self.dv)
 
     def plan_key(self):
-        return ("diff_attention", self.heads, self.nkv, self.window, self.kernel_family())
+        return ("diff_attention", self.heads, self.nkv, self.window, self.d, self.dv, self.rt is not None and self.rt.dtype)
 
     def planner(self, page_size: int, sm_count: int):
-        rows = {"mma": 64, "simt": ROW_TILE}[self.kernel_family(page_size)]
+        family = self.kernel_family(page_size)
+        if family == "tc":       # plain grouped-query attention over 2 x heads padded query maps
+            return AttentionPlanner(AttentionShape(self.nq, self.nkv, self.window, 128), sm_count)
+        rows = {"mma": 64, "simt": ROW_TILE}[family]
         return AttentionPlanner(AttentionShape(self.heads, self.nkv, self.window, rows), sm_count)
 
     def parameters(self):
@@ -106,12 +119,14 @@ class DifferentialAttention(Mixer):
         meta = cache.meta
         proj = rt.linear(h, self.weight, ws, "mm_proj", out_dtype=torch.float32)
         p = proj.tensor
-        q = ws.get("mm_q", (T, self.qw), rt.dtype)
+        family = self.kernel_family(cache.page_size)
+        padded = family == "tc"
+        q = ws.get("mm_q", (T, self.qw * (MAPS if padded else 1)), rt.dtype)
         rdim = int(getattr(self.position, "rotary_dim", 0) or 0)
         K.rope_append_maps(p, ctx.positions, ctx.tok_seg, meta["block_table"], self.position.inv_freq, rdim,
                            bool(getattr(self.position, "interleaved", False)), q, cache.storage, nq=self.nq,
                            nkv=self.nkv, kparts=MAPS, d=self.d, dv=self.dv, page_size=cache.page_size,
-                           nsplit=proj.nsplit, split_stride=proj.split_stride, status=ctx.status)
+                           nsplit=proj.nsplit, split_stride=proj.split_stride, status=ctx.status, q_pad=padded)
         maps = ws.get("mm_maps", (T, self.heads, MAPS, self.dv), torch.float32)     # a1, a2 of every head
         part_rows = max(1, meta["part_rows_cap"])
         part_acc = ws.get("attn_part_acc", (part_rows, self.nq, self.dv), torch.float32)
@@ -121,14 +136,30 @@ class DifferentialAttention(Mixer):
                       window=self.window or 0, scale=self.scale, kparts=MAPS, softcap=self.softcap)
         args = (q, cache.storage, maps, part_acc, part_ml)
         tail = (ctx.positions, meta["block_table"], meta["tok_part_row"])
-        if self.kernel_family(cache.page_size) == "mma":
+        big_items = meta["items"][n_small * ITEM_INTS:]
+        if family == "tc":
+            plain = dict(common, d=self.dv, kparts=1)         # keys as wide as values, one map per (padded) query head
+            if n_small:
+                chunks = -(-(self.nq // self.nkv) // ROW_TILE)
+                counters = ws.get_zeroed("attn_counters", (T * self.nkv * chunks,), torch.int32)
+                K.attention_mma_ext(*args, meta["items"], n_small, 16, *tail, **plain,
+                                    tok_nsplit=meta["tok_nsplit"], counters=counters)
+            if n_big:
+                K.attention_tc_ext(q, cache.storage, maps, big_items, n_big, ctx.positions, meta["block_table"],
+                                   nq=self.nq, nkv=self.nkv, d=self.dv, page_size=cache.page_size,
+                                   window=self.window or 0, scale=self.scale, status=ctx.status, part_acc=part_acc,
+                                   part_ml=part_ml, tok_part_row=meta["tok_part_row"], softcap=self.softcap)
+                if meta.get("big_split"):
+                    K.attention_combine(part_acc, part_ml, meta["tok_part_row"], meta["tok_nsplit"], maps,
+                                        nq=self.nq, d=self.dv)
+        elif family == "mma":
             if n_small:          # decoded tokens and short portions: 16-row tiles, key splits merged by the last CTA
                 chunks = -(-(self.heads // self.nkv) // ROW_TILE)
                 counters = ws.get_zeroed("attn_counters", (T * self.nkv * MAPS * chunks,), torch.int32)
                 K.attention_mma_ext(*args, meta["items"], n_small, 16, *tail, **common,
                                     tok_nsplit=meta["tok_nsplit"], counters=counters)
             if n_big:            # long portions: 64-row tiles
-                K.attention_mma_ext(*args, meta["items"][n_small * ITEM_INTS:], n_big, 64, *tail, **common)
+                K.attention_mma_ext(*args, big_items, n_big, 64, *tail, **common)
         else:
             n = n_small + n_big
             if n:
