@@ -149,7 +149,9 @@ attention_mma_kernel(const AttnArgs a) {
         constexpr int ITERS = KT * CPR / THREADS;
         const uint32_t kbase = kv_s + stage * (L::K_BYTES + L::V_BYTES);
         const uint32_t vbase = kbase + L::K_BYTES;
-#pragma unroll
+        // 16-row tiles serve a few key tiles per CTA: their time is the fetch of the kernel's instructions (ncu:
+        // 70 us whatever the work, stalled on "no instruction"), so their copies stay a loop instead of 16 bodies
+#pragma unroll (ROWS == 16 ? 2 : ITERS)
         for (int i = 0; i < ITERS; ++i) {
             const int c = i * THREADS + tid;
             const int j = c / CPR, ch = c % CPR;
@@ -177,7 +179,7 @@ attention_mma_kernel(const AttnArgs a) {
 
     constexpr int STAGES = L::STAGES;
     const int ntiles = (kv_end - kv_begin + KT - 1) / KT;
-#pragma unroll
+#pragma unroll 1
     for (int st = 0; st < STAGES - 1; ++st) {
         if (st < ntiles) load_tile(st, kv_begin + st * KT);
         cp_async_commit();

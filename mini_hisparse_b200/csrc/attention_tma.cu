@@ -50,7 +50,16 @@ struct AttnArgs {
     const float* gate;
     int gate_nsplit, gate_ld;
     size_t gate_split_stride;
+    int gate_per_head;          // the gate has one column per head instead of one per output element
+    int shared_kv;              // a latent cache: the pool is [pages][P][d] rows (one KV head), a row is key AND value
+    float softcap;              // s <- softcap * tanh(s / softcap) on the scaled score (0: none)
+    int out_f32;                // `out` is float32 (a sum of the outputs is still to be taken in 32 bits)
 };
+
+__device__ __forceinline__ void store_out(const AttnArgs& a, size_t idx, float v) {
+    if (a.out_f32) ((float*)a.out)[idx] = v;
+    else a.out[idx] = __float2bfloat16_rn(v);
+}
 
 __device__ __forceinline__ float gate_of(const AttnArgs& a, int t, int col) {
     if (!a.gate) return 1.f;
@@ -157,12 +166,14 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs 
             if (lane == 0) mbar_expect_tx(full_bar(stage), __popc(have) * 2 * a.P * D * 2);
             __syncwarp();
             if (page >= 0) {
-                const int row0 = ((page * 2) * a.nkv + kvh) * a.P;
+                const bool shared = EXT && a.shared_kv;
+                const int row0 = shared ? page * a.P : ((page * 2) * a.nkv + kvh) * a.P;
+                const int vrow0 = shared ? row0 : row0 + a.nkv * a.P;
                 const uint32_t dst = kv_s + stage * L::STAGE_BYTES + lane * a.P * 128;
 #pragma unroll
                 for (int h = 0; h < L::HALVES; ++h) {
                     tma_load_2d(dst + h * KT * 128, &kv_map, h * 64, row0, full_bar(stage));
-                    tma_load_2d(dst + L::KV_BYTES + h * KT * 128, &kv_map, h * 64, row0 + a.nkv * a.P, full_bar(stage));
+                    tma_load_2d(dst + L::KV_BYTES + h * KT * 128, &kv_map, h * 64, vrow0, full_bar(stage));
                 }
             }
             armed = itile + 1;
@@ -238,6 +249,15 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs 
                 ldmatrix_x4(swz(k_s, KT, r, c), b0, b1, b2, b3);
                 mma_bf16(s[j], qf[k], b0, b1);
                 mma_bf16(s[j], qf[k + 1], b2, b3);
+            }
+        }
+        if constexpr (EXT) {
+            if (a.softcap > 0.f) {      // the cap works on the scaled score; the tile stays in the raw products' units
+                const float to_cap = a.scale / a.softcap, from_cap = a.softcap / a.scale;
+#pragma unroll
+                for (int j = 0; j < NT; ++j)
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) s[j][x] = from_cap * tanhf(s[j][x] * to_cap);
             }
         }
         float mx[2] = {-INFINITY, -INFINITY};
@@ -353,8 +373,12 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs 
             const int t = tok0 + row / nheads, hq = kvh * groups + head0 + row % nheads;
             if (split < 0) {
                 float res = lsum > 0.f ? acc / lsum : 0.f;
-                if constexpr (EXT) res *= gate_of(a, t, hq * D + e);
-                a.out[((size_t)t * a.nq + hq) * D + e] = __float2bfloat16_rn(res);
+                if constexpr (EXT) {
+                    res *= gate_of(a, t, a.gate_per_head ? hq : hq * D + e);
+                    store_out(a, ((size_t)t * a.nq + hq) * D + e, res);
+                } else {
+                    a.out[((size_t)t * a.nq + hq) * D + e] = __float2bfloat16_rn(res);
+                }
             } else {
                 const size_t prow = (size_t)a.tok_part_row[t] + split;
                 a.part_acc[(prow * a.nq + hq) * D + e] = acc;
@@ -429,8 +453,18 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs 
                     }
                     const float inv = inv_s[row];
                     if constexpr (EXT) {
-                        acc.x *= gate_of(a, t, hq * D + e); acc.y *= gate_of(a, t, hq * D + e + 1);
-                        acc.z *= gate_of(a, t, hq * D + e + 2); acc.w *= gate_of(a, t, hq * D + e + 3);
+                        if (a.gate_per_head) {
+                            const float g = gate_of(a, t, hq);
+                            acc.x *= g; acc.y *= g; acc.z *= g; acc.w *= g;
+                        } else {
+                            acc.x *= gate_of(a, t, hq * D + e); acc.y *= gate_of(a, t, hq * D + e + 1);
+                            acc.z *= gate_of(a, t, hq * D + e + 2); acc.w *= gate_of(a, t, hq * D + e + 3);
+                        }
+                        if (a.out_f32) {
+                            *(float4*)((float*)a.out + ((size_t)t * a.nq + hq) * D + e) =
+                                make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+                            continue;
+                        }
                     }
                     uint2 packed;
                     packed.x = pack_bf16(acc.x * inv, acc.y * inv);
@@ -516,6 +550,7 @@ MHB_EXPORT int mhb_attention_tma(const void* q, const void* cache, void* out, fl
     a.width = width; a.nq = nq; a.nkv = nkv; a.P = P; a.num_pages = num_pages; a.window = window;
     a.scale = scale;
     a.fresh = fresh;
+    a.gate_per_head = 0; a.shared_kv = 0; a.softcap = 0.f; a.out_f32 = 0;
     a.sink = nullptr; a.gate = nullptr; a.gate_nsplit = 1; a.gate_ld = 0; a.gate_split_stride = 0;
     if (rows == 16) return d == 128 ? launch<128, 16, false>(map, a, launch_items, stream) : launch<64, 16, false>(map, a, launch_items, stream);
     return fail("attention_tma: tile height %d", rows);
@@ -528,13 +563,15 @@ MHB_EXPORT int mhb_attention_tma_ext(const void* q, const void* cache, void* out
                                      const int* tok_part_row, const int* tok_nsplit, int* counters, int nq, int nkv,
                                      int d, int P, int num_pages, int window, int fresh, float scale,
                                      const float* sink, const float* gate, int gate_nsplit,
-                                     long long gate_split_stride, int gate_ld, int* status, cudaStream_t stream) {
+                                     long long gate_split_stride, int gate_ld, int gate_per_head, int shared_kv,
+                                     float softcap, int out_f32, int* status, cudaStream_t stream) {
     if (launch_items <= 0) return 0;
     if (nkv <= 0 || nq % nkv) return fail("attention: %d query heads over %d KV heads", nq, nkv);
     if (!mhb_attention_tma_supports(d, P))
         return fail("attention_tma: head_dim %d with pages of %d keys is not built (head_dim 64 or 128, page size dividing 64)", d, P);
     if (sink && !(scale > 0.f)) return fail("attention_tma: a sink needs a positive scale");
-    const long long total_rows = (long long)num_pages * 2 * nkv * P;
+    if (shared_kv && nkv != 1) return fail("attention_tma: rows that are key and value at once have one KV head");
+    const long long total_rows = shared_kv ? (long long)num_pages * P : (long long)num_pages * 2 * nkv * P;
     if (total_rows > 0x7fffffffLL) return fail("attention_tma: the pool has too many rows for one tensor map");
     CUtensorMap map;
     int rc = make_bf16_map(&map, cache, total_rows, d, d, P);
@@ -548,6 +585,7 @@ MHB_EXPORT int mhb_attention_tma_ext(const void* q, const void* cache, void* out
     a.fresh = fresh;
     a.sink = sink; a.gate = gate; a.gate_nsplit = gate_nsplit; a.gate_ld = gate_ld;
     a.gate_split_stride = (size_t)gate_split_stride;
+    a.gate_per_head = gate_per_head; a.shared_kv = shared_kv; a.softcap = softcap; a.out_f32 = out_f32;
     if (rows == 16) return d == 128 ? launch<128, 16, true>(map, a, launch_items, stream) : launch<64, 16, true>(map, a, launch_items, stream);
     return fail("attention_tma: tile height %d", rows);
 }

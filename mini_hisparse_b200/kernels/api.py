@@ -670,9 +670,12 @@ def attention_tc(q, cache, out, items, num_items, positions, block_table, *, nq,
 
 def attention_tma_ext(q, cache, out, part_acc, part_ml, items, num_items, rows, positions, block_table,
                       tok_part_row, *, nq, nkv, d, page_size, window=0, scale=None, tok_nsplit=None,
-                      counters=None, status=None, fresh=0, sink=None, gate=None, gate_nsplit=1, gate_split_stride=0):
-    """attention_tma with a ``sink`` per query head, a ``gate`` on the output and softmax weights that keep 16
-    bits in the value product; keys and values are both ``d`` wide."""
+                      counters=None, status=None, fresh=0, sink=None, gate=None, gate_nsplit=1, gate_split_stride=0,
+                      gate_per_head=False, shared_kv=False, softcap=0.0):
+    """attention_tma with a ``sink`` per query head, a ``gate`` on the output (``gate_per_head``: one column per
+    head) and softmax weights that keep 16 bits in the value product; keys and values are both ``d`` wide.
+    ``shared_kv``: the pool is [pages, P, d] and a row is its position's key and value at once; ``softcap`` caps
+    the scaled scores; ``out`` may be float32."""
     lib = build.load("attention_tma")
     if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or not cache.is_contiguous():
         raise KernelError("attention_tma_ext: q and the (contiguous) pool must be bfloat16")
@@ -684,7 +687,9 @@ def attention_tma_ext(q, cache, out, part_acc, part_ml, items, num_items, rows, 
         c_int(num_items), c_int(rows), _ptr(positions), _ptr(block_table), c_int(block_table.shape[-1]),
         _ptr(tok_part_row), _ptr(tok_nsplit), _ptr(counters), c_int(nq), c_int(nkv), c_int(d),
         c_int(page_size), c_int(cache.shape[0]), c_int(window or 0), c_int(fresh), c_float(scale), _ptr(sink),
-        g[0], g[1], g[2], g[3], _ptr(status), _stream()), "attention_tma_ext")
+        g[0], g[1], g[2], g[3], c_int(1 if gate_per_head else 0), c_int(1 if shared_kv else 0),
+        c_float(softcap or 0.0), c_int(1 if out.dtype == torch.float32 else 0), _ptr(status), _stream()),
+        "attention_tma_ext")
 
 
 def attention_tc_ext(q, cache, out, items, num_items, positions, block_table, *, nq, nkv, d, page_size,

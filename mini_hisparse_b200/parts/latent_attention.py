@@ -70,7 +70,7 @@ class LatentAttention(Mixer):
         if self.kernel_family() == "simt":
             return ("attention_simt", "mixparts")
         if self.width in (64, 128):
-            return ("attention_simt", "attention_mma_ext", "attention_tc", "mixparts")
+            return ("attention_simt", "attention_mma_ext", "attention_tma", "attention_tc", "mixparts")
         return ("attention_simt", "attention_mma_ext", "mixparts")
 
     def cache_need(self):
@@ -129,8 +129,14 @@ class LatentAttention(Mixer):
             if n_small:          # decoded tokens and short portions: 16-row tiles, key splits merged by the last CTA
                 chunks = -(-self.heads // ROW_TILE)
                 counters = ws.get_zeroed("attn_counters", (T * chunks,), torch.int32)
-                K.attention_mma_ext(*args, meta["items"], n_small, 16, *tail, **common,
-                                    tok_nsplit=meta["tok_nsplit"], counters=counters)
+                if family == "tc":      # TMA-fed tiles
+                    K.attention_tma_ext(*args, meta["items"], n_small, 16, *tail, nq=self.heads, nkv=1, d=self.width,
+                                        page_size=cache.page_size, window=self.window or 0, scale=self.scale,
+                                        shared_kv=True, **gate, tok_nsplit=meta["tok_nsplit"], counters=counters,
+                                        status=ctx.status)
+                else:
+                    K.attention_mma_ext(*args, meta["items"], n_small, 16, *tail, **common,
+                                        tok_nsplit=meta["tok_nsplit"], counters=counters)
             big_items = meta["items"][n_small * ITEM_INTS:]
             if n_big and family == "tc":      # long portions: tcgen05 128-row tiles, split along the keys when few
                 K.attention_tc_ext(q_full, cache.storage, lat, big_items, n_big, ctx.positions, meta["block_table"],

@@ -83,7 +83,7 @@ class DifferentialAttention(Mixer):
         if self.kernel_family() == "simt":
             return ("attention_simt", "mixparts")
         if MAPS * self.d == self.dv and self.dv in (64, 128):
-            return ("attention_simt", "attention_mma_ext", "attention_tc", "mixparts")
+            return ("attention_simt", "attention_mma_ext", "attention_tma", "attention_tc", "mixparts")
         return ("attention_simt", "attention_mma_ext", "mixparts")
 
     def cache_need(self):
@@ -138,12 +138,13 @@ class DifferentialAttention(Mixer):
         tail = (ctx.positions, meta["block_table"], meta["tok_part_row"])
         big_items = meta["items"][n_small * ITEM_INTS:]
         if family == "tc":
-            plain = dict(common, d=self.dv, kparts=1)         # keys as wide as values, one map per (padded) query head
-            if n_small:
+            if n_small:          # decoded tokens and short portions: TMA-fed 16-row tiles, key splits merged by the last CTA
                 chunks = -(-(self.nq // self.nkv) // ROW_TILE)
                 counters = ws.get_zeroed("attn_counters", (T * self.nkv * chunks,), torch.int32)
-                K.attention_mma_ext(*args, meta["items"], n_small, 16, *tail, **plain,
-                                    tok_nsplit=meta["tok_nsplit"], counters=counters)
+                K.attention_tma_ext(*args, meta["items"], n_small, 16, *tail, nq=self.nq, nkv=self.nkv, d=self.dv,
+                                    page_size=cache.page_size, window=self.window or 0, scale=self.scale,
+                                    softcap=self.softcap, tok_nsplit=meta["tok_nsplit"], counters=counters,
+                                    status=ctx.status)
             if n_big:
                 K.attention_tc_ext(q, cache.storage, maps, big_items, n_big, ctx.positions, meta["block_table"],
                                    nq=self.nq, nkv=self.nkv, d=self.dv, page_size=cache.page_size,

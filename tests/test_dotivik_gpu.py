@@ -266,8 +266,15 @@ def attend(K, kernel, dtype, shape, segments, q_rows, pool, table, out_shape, ou
         if plan.n_small:
             counters = torch.zeros(T * opts["nkv"] * opts.get("kparts", 1) * -(-(shape.q_heads // shape.kv_heads) // 16),
                                    dtype=torch.int32, device="cuda")
-            K.attention_mma_ext(q_rows, pool, o, part_acc, part_ml, items, plan.n_small, 16, positions, tables, tpr,
-                                **opts, tok_nsplit=tns, counters=counters)
+            if kernel == "tc":          # TMA-fed 16-row tiles
+                status = torch.zeros(1, dtype=torch.int32, device="cuda")
+                tc = {k: v for k, v in opts.items() if k not in ("dv", "kparts")}
+                K.attention_tma_ext(q_rows, pool, o, part_acc, part_ml, items, plan.n_small, 16, positions, tables, tpr,
+                                    **tc, tok_nsplit=tns, counters=counters, status=status)
+                assert int(status) == 0
+            else:
+                K.attention_mma_ext(q_rows, pool, o, part_acc, part_ml, items, plan.n_small, 16, positions, tables, tpr,
+                                    **opts, tok_nsplit=tns, counters=counters)
             assert int(counters.abs().sum()) == 0
         if plan.n_big and kernel == "tc":
             status = torch.zeros(1, dtype=torch.int32, device="cuda")
