@@ -397,9 +397,15 @@ head_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, size_t xs_t, size_t 
         const int t = t0 + wrow + (lane >> 2) + 8 * half;
         if (t >= T) continue;
         OT* o = out + (size_t)t * os_t + (size_t)h * os_h;
+        // two neighbours in one store where the pair is whole and its address even
+        const bool pairs = sizeof(OT) == 2 && ((os_t | os_h) & 1) == 0 && ((uintptr_t)out & 3) == 0;
 #pragma unroll
         for (int j = 0; j < HM_N / 8; ++j) {
             const int n = n0 + j * 8 + (lane & 3) * 2;
+            if (pairs && n + 1 < N) {
+                *(uint32_t*)(o + n) = pack_bf16(acc[j][2 * half], acc[j][2 * half + 1]);
+                continue;
+            }
             if (n < N) o[n] = from_float<OT>(acc[j][2 * half]);
             if (n + 1 < N) o[n + 1] = from_float<OT>(acc[j][2 * half + 1]);
         }

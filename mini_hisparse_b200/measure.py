@@ -438,7 +438,8 @@ class KernelTimes:
 
     SKIP = {"stream_scope", "dtype_code", "stream_k_scratch", "gemm_tc_wait_limit", "KernelError",
             "attention_decode_supports", "attention_tma_supports", "gemm_tc_qkv_rope_supports",
-            "attention_decode_max_clusters", "lightning_chunk_smem"}
+            "attention_decode_max_clusters", "lightning_chunk_smem", "attention_mma_ext_supports",
+            "lightning_chunked_tc_supports"}
 
     def __enter__(self):
         self.saved, self.events = {}, []
