@@ -187,6 +187,33 @@ def test_layer_norm_adds_two_pending_products(H):
                                atol=3e-6, rtol=3e-6)
 
 
+def test_a_pair_of_pending_products_reaches_a_norm_that_adds_one():
+    """A parallel block leaves two products pending; a norm whose kernel adds one (the RMS norm of another
+    arrangement that may follow) settles the second into the stream first."""
+    from mini_hisparse_b200.engine.engine import make_runtime
+    from mini_hisparse_b200.parts.base import Product, StepContext, Workspace
+    from mini_hisparse_b200.parts.registry import NORMS
+    from mini_hisparse_b200.parts.spec import PartSpec
+
+    g = torch.Generator().manual_seed(6)
+    T, H = 5, 72
+    x, a, f = (torch.randn(T, H, generator=g) for _ in range(3))
+    parts = torch.randn(2, T, H, generator=g)
+    w = 1 + 0.1 * torch.randn(H, generator=g)
+    rt = make_runtime("cuda:0", "float32")
+    ctx = StepContext(rt=rt, ws=Workspace(rt.device), T=T, segments=[], tokens=None, positions=None, tok_seg=None,
+                      seg_slot=None, status=None)
+    norm = NORMS.build(PartSpec.make("rmsnorm", width=H, eps=1e-5), rt=rt)
+    norm.load({"weight": w.cuda()})
+    xd = x.cuda().clone()
+    pending = Product(a.cuda(), 1, also=Product(parts.cuda(), 2, also=Product(f.cuda())))
+    out = norm.forward(xd, ctx, delta=pending)
+    total = x.double() + a.double() + parts.double().sum(0) + f.double()
+    torch.testing.assert_close(xd.cpu().double(), total, atol=3e-6, rtol=3e-6)
+    torch.testing.assert_close(out.cpu().double(), P.unit_rms(total, 1e-5) * w.double(), atol=3e-6, rtol=3e-6)
+    torch.testing.assert_close(pending.reduced().cpu().double(), total - x.double(), atol=3e-6, rtol=3e-6)
+
+
 def test_stream_packing_and_gated_activation():
     from mini_hisparse_b200.kernels import api as K
 
