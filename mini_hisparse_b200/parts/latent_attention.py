@@ -50,7 +50,7 @@ class LatentAttention(Mixer):
 
     def kernel_family(self, page_size: int | None = None) -> str:
         """"tc": tcgen05 128-row tiles for long portions (bfloat16, a cache row 64 or 128 wide, pages that divide
-        64) and mma.sync 16-row tiles for the rest; "mma": mma.sync tiles of 64 and 16 rows (bfloat16, a cache
+        64) and TMA-fed 16-row tiles for the rest; "mma": mma.sync tiles of 64 and 16 rows (bfloat16, a cache
         row of at most 128 elements, a multiple of 8 like the latent); "simt": the CUDA cores (float32, and every
         other width)."""
         if (self.rt is None or self.rt.dtype != torch.bfloat16 or not self.scale > 0.0

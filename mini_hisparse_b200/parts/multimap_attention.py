@@ -68,7 +68,7 @@ class DifferentialAttention(Mixer):
         """"tc": the two maps' keys of a KV head lie side by side and are as wide together as its values (64 or 128,
         bfloat16, pages that divide 64): every q map is padded with zeros to that width, at its own map's columns,
         so a map's score is the product with the WHOLE key row and the kernels see plain grouped-query attention
-        with 2 x heads query heads: tcgen05 128-row tiles for long portions, mma.sync 16-row tiles for the rest.
+        with 2 x heads query heads: tcgen05 128-row tiles for long portions, TMA-fed 16-row tiles for the rest.
         "mma": mma.sync tiles of 64 and 16 rows that read a map's keys at its columns (bfloat16, widths that are
         multiples of 8 up to 128); "simt": the CUDA cores (float32, and every other width)."""
         if (self.rt is None or self.rt.dtype != torch.bfloat16 or not self.scale > 0.0
