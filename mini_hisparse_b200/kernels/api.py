@@ -528,9 +528,6 @@ def lightning_chunked_tc(proj, q0, k0, v0, decay, state, out, tok_seg, seg_slot,
            "lightning_chunked_tc")
 
 
-MMA_EXT_GENERAL = True      # the tensor-core attention takes score maps, a cap, shared rows and float32 outputs
-
-
 def attention_mma_ext_supports(d: int, dv: int) -> bool:
     """Widths of keys and values the tensor-core attention with options takes (tiles padded to multiples of 32)."""
     return 8 <= d <= 128 and d % 8 == 0 and 8 <= dv <= 128 and dv % 8 == 0
