@@ -23,6 +23,7 @@ namespace {
 template <typename T>
 __device__ __forceinline__ float load_parts(const T* p, size_t idx, int nsplit, size_t split_stride) {
     float v = to_float(p[idx]);
+#pragma unroll 4              // the parts' loads in flight together; they are still added in order
     for (int s = 1; s < nsplit; ++s) v += to_float(p[idx + (size_t)s * split_stride]);
     return v;
 }
@@ -57,11 +58,15 @@ __global__ void add_layernorm_kernel(float* __restrict__ x, const DT* __restrict
         const float* f2 = (const float*)d2;
         for (int i = 4 * threadIdx.x; i < H; i += 4 * blockDim.x) {
             float4 v = *(const float4*)(xr + i);
-            if (f1) for (int p = 0; p < n1; ++p) {
+            if (f1)
+#pragma unroll 4
+            for (int p = 0; p < n1; ++p) {
                 const float4 a = *(const float4*)(f1 + (size_t)p * s1 + (size_t)s * H + i);
                 v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
             }
-            if (f2) for (int p = 0; p < n2; ++p) {
+            if (f2)
+#pragma unroll 4
+            for (int p = 0; p < n2; ++p) {
                 const float4 a = *(const float4*)(f2 + (size_t)p * s2 + (size_t)s * H + i);
                 v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
             }
